@@ -1,0 +1,449 @@
+// Persistent grouped FP8 GEMMs on the 5th-generation tensor core (tcgen05), sm_100a.
+//
+//   MODE 1  GEMM1 + SwiGLU:  G = A_sorted[R,7168] x W13[e]^T, promoted with a_scale[row,kb] * w13_scale[e,nb,kb] every
+//           128 K; inter = silu(G[:, 2048+n]) * G[:, n]; inter is re-quantised per row per 128 columns into TWO e4m3
+//           terms with one shared scale (value + residual), so GEMM2 stays on the FP8 pipe at ~bf16 accuracy.
+//           Reference: _fused_moe_gemm1_swiglu_kernel (solution/python/pure_triton_impl.py:886-1046), oracle math
+//           solution/cuda/binding.py:166-175.
+//   MODE 2  GEMM2:  O = inter[R,2048] x W2[e]^T, both e4m3 terms accumulate into the same TMEM tile, promoted with
+//           inter_scale[row,kb] * w2_scale[e,nb,kb]; bf16 rows out.
+//           Reference: _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196), oracle math
+//           solution/cuda/binding.py:178-179.
+//
+// Tile: 128 sorted rows x 256 accumulator columns, K chunk = 128 bytes = one quantisation block = one 128-byte swizzle
+// row.  MODE 1 uses two 128-row weight boxes per chunk (W1 rows n0.., W3 rows 2048+n0..) laid out back to back so a
+// single N=256 MMA produces both SwiGLU operands; MODE 2 uses one 256-row box of W2 and two A boxes (the two terms).
+//
+// Warp roles (320 threads): warps 0-7 promote TMEM partials into fp32 registers and run the epilogue (warp w owns TMEM
+// lanes 32*(w%4).. and half of the columns), warp 8 issues TMA loads, warp 9 owns TMEM and issues the MMAs.
+// fp32 block scales are not power-of-two, so the hardware block-scaled MMA cannot apply them: each 128-K chunk is
+// accumulated on its own into one of two 256-column TMEM stages and folded into registers with one FMA per element
+// while the next chunk's MMAs run into the other stage.
+//
+// Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the CTA records the failure in the status word,
+// raises a CTA-wide abort flag, drains its outstanding TMA loads, frees TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int TILE_N = 256;                    // TMEM columns per accumulator stage
+constexpr int A_TILE_BYTES = BLOCK_M * 128;    // 16 KB
+constexpr int B_TILE_BYTES = TILE_N * 128;     // 32 KB
+constexpr int NUM_PROMO_WARPS = 8;
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int GEMM_THREADS = 320;
+
+template <int MODE>
+struct Cfg {
+  static constexpr int A_TILES = (MODE == 1) ? 1 : 2;
+  static constexpr int STAGES = (MODE == 1) ? 4 : 3;
+  static constexpr int K_CHUNKS = (MODE == 1) ? H_BLOCKS : I_BLOCKS;
+  static constexpr int N_TILES = (MODE == 1) ? (I / 128) : (H / 256);  // 16, 28
+  static constexpr int STAGE_BYTES = A_TILES * A_TILE_BYTES + B_TILE_BYTES;
+};
+
+struct GemmArgs {
+  const int* block_offsets;  // [E+1]
+  const int* counts;         // [E]
+  const float* row_scale;    // MODE1: a_scale_sorted [56,R_max]; MODE2: inter_scale [16,R_max]
+  const float* w_scale;      // MODE1: [E,32,56]; MODE2: [E,56,16]
+  uint8_t* inter_q;          // MODE1 out: [2,R_max,2048]
+  float* inter_scale;        // MODE1 out: [16,R_max]
+  uint16_t* expert_out;      // MODE2 out: [R_max,7168] bf16
+  int* status;
+  int E_local;
+  int R_max;
+};
+
+struct TileInfo {
+  int e, nt, mblk, m_local, cnt;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_off, const int* s_cnt, int E, int NT) {
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (s_off[mid] * NT <= tile) lo = mid; else hi = mid - 1;
+  }
+  TileInfo ti;
+  ti.e = lo;
+  int local = tile - s_off[lo] * NT;
+  int mb = s_off[lo + 1] - s_off[lo];
+  ti.nt = local / mb;
+  ti.m_local = local - ti.nt * mb;
+  ti.mblk = s_off[lo] + ti.m_local;
+  ti.cnt = s_cnt[lo];
+  return ti;
+}
+
+struct __align__(8) GemmAux {
+  uint64_t full[4];
+  uint64_t empty[4];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint64_t xbar[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int off[E_GLOBAL + 1];
+  int cnt[E_GLOBAL];
+  float amax[2][2][BLOCK_M];
+};
+
+template <int MODE>
+constexpr size_t gemm_smem_bytes() {
+  return 1024 + static_cast<size_t>(Cfg<MODE>::STAGES) * Cfg<MODE>::STAGE_BYTES + sizeof(GemmAux);
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ void unpack4_e4m3(uint32_t v, float (&f)[4]) {
+  __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v & 0xffffu), __NV_E4M3);
+  __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v >> 16), __NV_E4M3);
+  float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+  float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs args) {
+  using C = Cfg<MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  GemmAux* aux = reinterpret_cast<GemmAux*>(tiles_ptr + C::STAGES * C::STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int E = args.E_local;
+  constexpr int NT = C::N_TILES;
+
+  for (int i = threadIdx.x; i <= E; i += GEMM_THREADS) aux->off[i] = __ldg(args.block_offsets + i);
+  for (int i = threadIdx.x; i < E; i += GEMM_THREADS) aux->cnt[i] = __ldg(args.counts + i);
+  if (threadIdx.x == 0) aux->abort_flag = 0;
+
+  if (warp == PRODUCER_WARP && lane == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&aux->full[s]), 1);
+      mbar_init(smem_u32(&aux->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&aux->tfull[a]), 1);
+      mbar_init(smem_u32(&aux->tempty[a]), NUM_PROMO_WARPS);
+      mbar_init(smem_u32(&aux->xbar[a]), NUM_PROMO_WARPS);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(&aux->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = aux->tmem_base;
+  const int total_tiles = aux->off[E] * NT;
+  volatile int* abort_flag = &aux->abort_flag;
+
+  if (warp == PRODUCER_WARP) {
+    // ------------------------------------------------------------------ TMA producer (lane 0 issues, warp stays converged)
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
+      for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, abort_flag, args.status, 1, kb));
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = smem_u32(&aux->full[stage]);
+          const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+          if (MODE == 1) {
+            tma_load_2d(sbase, &tmA, full, kb * 128, ti.mblk * BLOCK_M);
+            tma_load_2d(sbase + A_TILE_BYTES, &tmB, full, kb * 128, ti.e * (2 * I) + ti.nt * 128);
+            tma_load_2d(sbase + A_TILE_BYTES + 128 * 128, &tmB, full, kb * 128, ti.e * (2 * I) + I + ti.nt * 128);
+          } else {
+            tma_load_2d(sbase, &tmA, full, kb * 128, ti.mblk * BLOCK_M);
+            tma_load_2d(sbase + A_TILE_BYTES, &tmA, full, kb * 128, args.R_max + ti.mblk * BLOCK_M);
+            tma_load_2d(sbase + 2 * A_TILE_BYTES, &tmB, full, kb * 128, ti.e * H + ti.nt * TILE_N);
+          }
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok && lane == 0) {
+      // Drain: every load already issued completes on its own; wait (bounded) so none lands after the CTA exits.
+      for (int s = 0; s < C::STAGES; ++s) {
+        long long n_s = issued / C::STAGES + ((issued % C::STAGES) > s ? 1 : 0);  // loads issued to stage s
+        if (n_s == 0) continue;
+        uint32_t par = static_cast<uint32_t>((n_s - 1) & 1);
+        for (int spin = 0; spin < (1 << 20); ++spin)
+          if (mbar_try_wait(smem_u32(&aux->full[s]), par)) break;
+      }
+    }
+    __syncwarp();
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer (lane 0 issues, warp stays converged)
+    constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M, TILE_N);
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb) &&
+                            mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb));
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
+          const uint32_t d = tmem_base + static_cast<uint32_t>(acc * TILE_N);
+          const uint64_t a0 = umma_desc_sw128(sbase);
+          const uint64_t b0 = umma_desc_sw128(sbase + C::A_TILES * A_TILE_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a0 + 2 * k4, b0 + 2 * k4, IDESC, k4 > 0 ? 1u : 0u);
+          if (MODE == 2) {
+            const uint64_t a1 = umma_desc_sw128(sbase + A_TILE_BYTES);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a1 + 2 * k4, b0 + 2 * k4, IDESC, 1u);
+          }
+          tc_commit(smem_u32(&aux->empty[stage]));
+          tc_commit(smem_u32(&aux->tfull[acc]));
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ promotion + epilogue (8 warps)
+    const int q = warp & 3;       // TMEM lane quarter this warp may read
+    const int h = warp >> 2;      // column half
+    const int r_in_tile = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+      const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
+      const int row = ti.mblk * BLOCK_M + r_in_tile;
+      const bool valid = (ti.m_local * BLOCK_M + r_in_tile) < ti.cnt;
+      const float* rs_ptr = args.row_scale + row;
+      const float* ws0_ptr;
+      const float* ws1_ptr;
+      if (MODE == 1) {
+        ws0_ptr = args.w_scale + (static_cast<size_t>(ti.e) * 32 + ti.nt) * H_BLOCKS;
+        ws1_ptr = args.w_scale + (static_cast<size_t>(ti.e) * 32 + 16 + ti.nt) * H_BLOCKS;
+      } else {
+        ws0_ptr = args.w_scale + (static_cast<size_t>(ti.e) * H_BLOCKS + ti.nt * 2 + h) * I_BLOCKS;
+        ws1_ptr = ws0_ptr;
+      }
+      float accs[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) accs[j] = 0.f;
+
+      float rs_n = __ldg(rs_ptr);
+      float w0_n = __ldg(ws0_ptr);
+      float w1_n = __ldg(ws1_ptr);
+      for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
+        const float sc0 = rs_n * w0_n;
+        const float sc1 = rs_n * w1_n;
+        if (kb + 1 < C::K_CHUNKS) {
+          rs_n = __ldg(rs_ptr + static_cast<size_t>(kb + 1) * args.R_max);
+          w0_n = __ldg(ws0_ptr + kb + 1);
+          w1_n = __ldg(ws1_ptr + kb + 1);
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tfull[acc]), acc_phase, abort_flag, args.status, 4, kb));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * TILE_N) + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          // MODE 1: columns [64h,64h+64) hold W1 ("up"), [128+64h, 128+64h+64) hold W3 ("gate").
+          const int col = (MODE == 1) ? ((i >> 1) * 128 + h * 64 + (i & 1) * 32) : (h * 128 + i * 32);
+          const float sc = (MODE == 1 && i >= 2) ? sc1 : sc0;
+          uint32_t tmp[32];
+          tmem_ld32(taddr + static_cast<uint32_t>(col), tmp);
+          tc_wait_ld();
+          if (i == 3) {
+            // all of this warp's reads of the stage are complete: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[acc]));
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) accs[i * 32 + j] = fmaf(__uint_as_float(tmp[j]), sc, accs[i * 32 + j]);
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) break;
+
+      if (MODE == 1) {
+        // accs[0..63] = up (W1) columns 64h.., accs[64..127] = gate (W3) for the same columns.
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          accs[j] = silu_mul(accs[64 + j], accs[j]);
+          amax = fmaxf(amax, fabsf(accs[j]));
+        }
+        float* ex = &aux->amax[tile_iter & 1][0][0];
+        ex[h * BLOCK_M + r_in_tile] = amax;
+        // the other column half of each row lives in warp (w ^ 4): exchange through shared memory, bounded wait
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&aux->xbar[tile_iter & 1]));
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->xbar[tile_iter & 1]), (tile_iter >> 1) & 1, abort_flag,
+                                               args.status, 5, tile_iter));
+        if (!ok) break;
+        amax = fmaxf(ex[r_in_tile], ex[BLOCK_M + r_in_tile]);
+        const float s = fmaxf(amax, 1e-20f) * (1.0f / 448.0f);
+        const float inv = 1.0f / s;
+        if (valid) {
+          uint8_t* q1p = args.inter_q + static_cast<size_t>(row) * I + ti.nt * 128 + h * 64;
+          uint8_t* q2p = q1p + static_cast<size_t>(args.R_max) * I;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w1[4], w2[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int j = v * 16 + u * 4;
+              w1[u] = pack4_e4m3(accs[j] * inv, accs[j + 1] * inv, accs[j + 2] * inv, accs[j + 3] * inv);
+              float back[4];
+              unpack4_e4m3(w1[u], back);
+              w2[u] = pack4_e4m3((accs[j] - back[0] * s) * inv, (accs[j + 1] - back[1] * s) * inv,
+                                 (accs[j + 2] - back[2] * s) * inv, (accs[j + 3] - back[3] * s) * inv);
+            }
+            reinterpret_cast<uint4*>(q1p)[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+            reinterpret_cast<uint4*>(q2p)[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+          }
+          if (h == 0) args.inter_scale[static_cast<size_t>(ti.nt) * args.R_max + row] = s;
+        }
+      } else {
+        if (valid) {
+          uint16_t* op = args.expert_out + static_cast<size_t>(row) * H + ti.nt * TILE_N + h * 128;
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            uint32_t o[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(accs[v * 8 + u * 2], accs[v * 8 + u * 2 + 1]);
+              o[u] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            reinterpret_cast<uint4*>(op)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Host side: tensor maps and launches
+// ---------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D byte tensor [rows, cols] (row pitch = cols), box [box_rows, 128 bytes], 128-byte swizzle.
+static int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return record_cuda_error(cudaErrorNotSupported);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue);
+  return B200MOE_OK;
+}
+
+template <int MODE>
+static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+  if (p->T == 0) return B200MOE_OK;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  B200MOE_CUDA_TRY(cudaGetDevice(&dev));
+  constexpr size_t smem = gemm_smem_bytes<MODE>();
+  if (dev < 64 && !attr_set[dev]) {
+    B200MOE_CUDA_TRY(cudaFuncSetAttribute(k_grouped_gemm<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  GemmArgs a;
+  a.block_offsets = ws->block_offsets;
+  a.counts = ws->counts;
+  a.inter_q = ws->inter_q;
+  a.inter_scale = ws->inter_scale;
+  a.expert_out = ws->expert_out;
+  a.status = ws->status;
+  a.E_local = p->E_local;
+  a.R_max = ws->R_max;
+  if (MODE == 1) {
+    if ((rc = make_map_u8(&tmA, ws->a_sorted, static_cast<uint64_t>(ws->R_max), H, BLOCK_M))) return rc;
+    if ((rc = make_map_u8(&tmB, p->gemm1_weights, static_cast<uint64_t>(p->E_local) * 2 * I, H, 128))) return rc;
+    a.row_scale = ws->a_scale_sorted;
+    a.w_scale = p->gemm1_weights_scale;
+  } else {
+    if ((rc = make_map_u8(&tmA, ws->inter_q, static_cast<uint64_t>(ws->R_max) * 2, I, BLOCK_M))) return rc;
+    if ((rc = make_map_u8(&tmB, p->gemm2_weights, static_cast<uint64_t>(p->E_local) * H, I, TILE_N))) return rc;
+    a.row_scale = ws->inter_scale;
+    a.w_scale = p->gemm2_weights_scale;
+  }
+  k_grouped_gemm<MODE><<<num_sms, GEMM_THREADS, smem, st>>>(tmA, tmB, a);
+  B200MOE_CUDA_TRY(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int launch_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+  return launch_gemm<1>(p, ws, num_sms, st);
+}
+int launch_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+  return launch_gemm<2>(p, ws, num_sms, st);
+}
+
+}  // namespace b200moe

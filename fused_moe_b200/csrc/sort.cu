@@ -1,0 +1,216 @@
+// Stable token ranking, BLOCK_M-padded expert layout, scatter, activation gather and the weighted top-8 reduce.
+//
+// What is produced equals the reference's sort metadata (solution/python/pure_triton_impl.py:474-551): padded
+// per-expert segments, block_offsets in units of BLOCK_M rows, pad rows carrying token id T and weight 0,
+// scatter_map = -1 for non-local pairs.  The ORDER inside an expert segment is ascending token id, which is what a
+// stable sort of the flat (token*8+k) list by expert gives (solution/cuda/binding.py:138-150); the reference's
+// Triton kernels take their positions from atomics and are not reproducible from run to run.
+//
+// A token selects an expert at most once, so the rank of pair (t, e) inside expert e is the number of earlier
+// tokens that selected e.  chunk_bits[c][e] holds that selection as one bit per token of 32-token chunk c; the rank
+// is chunk_base[c][e] + popc(bits & lanes_below).
+#include "common.cuh"
+
+namespace b200moe {
+
+// One warp per local expert: exclusive prefix of popc(chunk_bits[:, e]) over chunks.
+__global__ void __launch_bounds__(1024)
+k_rank_scan(const uint32_t* __restrict__ chunk_bits, int n_chunks, int E_local, int* __restrict__ chunk_base,
+            int* __restrict__ counts) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E_local) return;
+  int running = 0;
+  for (int base = 0; base < n_chunks; base += 32) {
+    int c = base + lane;
+    int v = (c < n_chunks) ? __popc(__ldg(chunk_bits + static_cast<size_t>(c) * E_local + e)) : 0;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (c < n_chunks) chunk_base[static_cast<size_t>(c) * E_local + e] = running + incl - v;
+    running += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) counts[e] = running;
+}
+
+// Padded layout (every CTA recomputes it in shared memory; CTA 0 publishes it) and the scatter, one warp per chunk.
+__global__ void __launch_bounds__(128)
+k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, const uint32_t* __restrict__ chunk_bits,
+          const int* __restrict__ chunk_base, const int* __restrict__ counts, int T, int local_offset, int E_local,
+          int n_chunks, int* __restrict__ block_offsets, int* __restrict__ total_blocks,
+          int* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights, int* __restrict__ scatter_map) {
+  __shared__ int s_row_base[E_GLOBAL + 1];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+
+  if (warp == 0) {
+    // lane handles experts [8*lane, 8*lane+8)
+    int blocks[8];
+    int local = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      int c = (e < E_local) ? __ldg(counts + e) : 0;
+      blocks[i] = (c + BLOCK_M - 1) / BLOCK_M;
+      local += blocks[i];
+    }
+    int incl = local;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    int run = incl - local;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int e = lane * 8 + i;
+      if (e < E_local) s_row_base[e] = run;  // in blocks
+      run += blocks[i];
+    }
+    if (lane == 31) s_row_base[E_local] = incl;  // total blocks
+  }
+  __syncthreads();
+  const int tot_blocks = s_row_base[E_local];
+
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e <= E_local; e += blockDim.x) block_offsets[e] = s_row_base[e];
+    if (threadIdx.x == 0) *total_blocks = tot_blocks;
+  }
+  // pad rows: expert e is handled by CTA (e mod gridDim)
+  for (int e = blockIdx.x; e < E_local; e += gridDim.x) {
+    int begin = s_row_base[e] * BLOCK_M + __ldg(counts + e);
+    int end = s_row_base[e + 1] * BLOCK_M;
+    for (int r = begin + threadIdx.x; r < end; r += blockDim.x) {
+      sorted_token_ids[r] = T;
+      sorted_weights[r] = 0.f;
+    }
+  }
+
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (chunk >= n_chunks) return;
+  const int t = chunk * 32 + lane;
+  if (t >= T) return;
+  const uint32_t below = (1u << lane) - 1u;
+  int dest[TOP_K];
+#pragma unroll
+  for (int k = 0; k < TOP_K; ++k) {
+    int le = __ldg(topk_idx + static_cast<size_t>(t) * TOP_K + k) - local_offset;
+    dest[k] = -1;
+    if (le >= 0 && le < E_local) {
+      uint32_t bits = __ldg(chunk_bits + static_cast<size_t>(chunk) * E_local + le);
+      int rank = __ldg(chunk_base + static_cast<size_t>(chunk) * E_local + le) + __popc(bits & below);
+      int d = s_row_base[le] * BLOCK_M + rank;
+      dest[k] = d;
+      sorted_token_ids[d] = t;
+      sorted_weights[d] = __ldg(topk_w + static_cast<size_t>(t) * TOP_K + k);
+    }
+  }
+  int4* out = reinterpret_cast<int4*>(scatter_map + static_cast<size_t>(t) * TOP_K);
+  out[0] = make_int4(dest[0], dest[1], dest[2], dest[3]);
+  out[1] = make_int4(dest[4], dest[5], dest[6], dest[7]);
+}
+
+// Copy the e4m3 row and the 56 scales of each real sorted row; pad rows are left as they are (their products are
+// never read).  One warp per row, grid-stride over the rows that exist.
+__global__ void __launch_bounds__(256)
+k_gather(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, int T,
+         const int* __restrict__ sorted_token_ids, const int* __restrict__ total_blocks, int R_max,
+         uint8_t* __restrict__ a_sorted, float* __restrict__ a_scale_sorted) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int rows = __ldg(total_blocks) * BLOCK_M;
+  for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
+    int tok = __ldg(sorted_token_ids + r);
+    if (tok >= T) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
+    uint4* dst = reinterpret_cast<uint4*>(a_sorted + static_cast<size_t>(r) * H);
+#pragma unroll
+    for (int i = 0; i < H / 16 / 32; ++i) dst[i * 32 + lane] = __ldg(src + i * 32 + lane);
+    for (int kb = lane; kb < H_BLOCKS; kb += 32)
+      a_scale_sorted[static_cast<size_t>(kb) * R_max + r] = __ldg(hidden_scale + static_cast<size_t>(kb) * T + tok);
+  }
+}
+
+// out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
+__global__ void __launch_bounds__(128)
+k_reduce(const uint16_t* __restrict__ expert_out, const int* __restrict__ scatter_map,
+         const float* __restrict__ topk_w, int T, uint16_t* __restrict__ out) {
+  const int t = blockIdx.x;
+  __shared__ int s_pos[TOP_K];
+  __shared__ float s_w[TOP_K];
+  if (threadIdx.x < TOP_K) {
+    s_pos[threadIdx.x] = __ldg(scatter_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
+    s_w[threadIdx.x] = __ldg(topk_w + static_cast<size_t>(t) * TOP_K + threadIdx.x);
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < TOP_K; ++k) {
+      int pos = s_pos[k];
+      if (pos < 0) continue;
+      float w = s_w[k];
+      uint4 q = __ldg(reinterpret_cast<const uint4*>(expert_out + static_cast<size_t>(pos) * H) + v);
+      uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = fmaf(w, __uint_as_float(u[j] << 16), acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, __uint_as_float(u[j] & 0xffff0000u), acc[2 * j + 1]);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      o[j] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
+  const int* idx = p->routing_logits ? ws->topk_idx : p->topk_idx_in;
+  const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
+  if (p->T == 0) {
+    B200MOE_CUDA_TRY(cudaMemsetAsync(ws->block_offsets, 0, sizeof(int) * (p->E_local + 1), st));
+    B200MOE_CUDA_TRY(cudaMemsetAsync(ws->total_blocks, 0, sizeof(int), st));
+    B200MOE_CUDA_TRY(cudaMemsetAsync(ws->counts, 0, sizeof(int) * p->E_local, st));
+    return B200MOE_OK;
+  }
+  int scan_grid = (p->E_local + 31) / 32;
+  k_rank_scan<<<scan_grid, 1024, 0, st>>>(ws->chunk_bits, ws->n_chunks, p->E_local, ws->chunk_base, ws->counts);
+  B200MOE_CUDA_TRY(cudaGetLastError());
+  int grid = (ws->n_chunks + 3) / 4;
+  k_scatter<<<grid, 128, 0, st>>>(idx, w, ws->chunk_bits, ws->chunk_base, ws->counts, p->T, p->local_expert_offset,
+                                  p->E_local, ws->n_chunks, ws->block_offsets, ws->total_blocks,
+                                  ws->sorted_token_ids, ws->sorted_weights, ws->scatter_map);
+  B200MOE_CUDA_TRY(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+  if (p->T == 0) return B200MOE_OK;
+  long long max_rows = ws->R_max;
+  int grid = static_cast<int>((max_rows + 7) / 8);
+  if (grid > num_sms * 8) grid = num_sms * 8;
+  if (grid < 1) grid = 1;
+  k_gather<<<grid, 256, 0, st>>>(p->hidden_states, p->hidden_states_scale, p->T, ws->sorted_token_ids,
+                                 ws->total_blocks, ws->R_max, ws->a_sorted, ws->a_scale_sorted);
+  B200MOE_CUDA_TRY(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
+  if (p->T == 0) return B200MOE_OK;
+  const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
+  k_reduce<<<p->T, 128, 0, st>>>(ws->expert_out, ws->scatter_map, w, p->T, p->output);
+  B200MOE_CUDA_TRY(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+}  // namespace b200moe

@@ -1,0 +1,248 @@
+"""Drop-in entry point: the DeepSeek-V3 FP8 block-scale fused MoE layer on B200.
+
+``kernel(...)`` keeps the signature, argument meaning and return convention of the reference entry point
+(solution/python/kernel.py:71-83; host orchestration solution/python/pure_triton_impl.py:2125-2403): ten inputs plus
+an optional destination ``output``; the bf16 ``[T, 7168]`` result is always returned.  Everything on the device is
+done by libb200moe.so through its C ABI (include/b200moe.h); PyTorch only provides device memory and the stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+H = 7168
+I = 2048
+E_GLOBAL = 256
+TOP_K = 8
+BLOCK_M = 128
+H_BLOCKS = H // 128
+I_BLOCKS = I // 128
+
+_FP8 = torch.float8_e4m3fn
+
+
+@dataclass
+class _Workspace:
+    """One carved view of the per-device scratch buffer, for exactly (T, E_local)."""
+
+    struct: _lib.Workspace
+    base_ptr: int
+    buffer: torch.Tensor
+
+    def view(self, name: str, dtype: torch.dtype, shape: Tuple[int, ...]) -> torch.Tensor:
+        """Torch view (no copy) of one workspace array; for tests and debugging."""
+        ptr = getattr(self.struct, name)
+        off = ptr - self.base_ptr
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.buffer[off:off + nbytes].view(dtype).view(*shape)
+
+
+@dataclass
+class _DeviceState:
+    buffer: Optional[torch.Tensor] = None
+    carved: Dict[Tuple[int, int], _Workspace] = field(default_factory=dict)
+    active: Optional[Tuple[int, int]] = None
+
+
+_devices: Dict[int, _DeviceState] = {}
+_host_scalar_cache: Dict[tuple, object] = {}
+
+
+def _host_scalar(x, cast):
+    """Python scalar from a scalar or a 0-d tensor; a device tensor is read back once per (address, dtype), as the
+    reference does (solution/python/pure_triton_impl.py:2012-2020)."""
+    if torch.is_tensor(x):
+        key = (x.data_ptr(), str(x.device), str(x.dtype), cast.__name__)
+        if key not in _host_scalar_cache:
+            _host_scalar_cache[key] = cast(x.item())
+        return _host_scalar_cache[key]
+    return cast(x)
+
+
+def workspace_bytes(T: int, E_local: int) -> int:
+    n = C.c_size_t(0)
+    _lib.check(_lib.load().b200moe_workspace_bytes(T, E_local, C.byref(n)), "b200moe_workspace_bytes")
+    return n.value
+
+
+def _workspace(device: torch.device, T: int, E_local: int, stream_ptr: int) -> _Workspace:
+    lib = _lib.load()
+    st = _devices.setdefault(device.index, _DeviceState())
+    need = workspace_bytes(T, E_local)
+    if st.buffer is None or st.buffer.numel() < need:
+        st.buffer = torch.empty(need, dtype=torch.uint8, device=device)
+        st.carved.clear()
+        st.active = None
+    key = (T, E_local)
+    ws = st.carved.get(key)
+    if ws is None:
+        s = _lib.Workspace()
+        base = st.buffer.data_ptr()
+        _lib.check(lib.b200moe_workspace_carve(base, st.buffer.numel(), T, E_local, C.byref(s)),
+                   "b200moe_workspace_carve")
+        ws = _Workspace(struct=s, base_ptr=base, buffer=st.buffer)
+        st.carved[key] = ws
+    if st.active != key:
+        # the status word sits at a (T, E_local)-dependent offset of the shared buffer
+        _lib.check(lib.b200moe_workspace_init(C.byref(ws.struct), stream_ptr), "b200moe_workspace_init")
+        st.active = key
+    return ws
+
+
+def _require(t: torch.Tensor, name: str, dtype: torch.dtype, shape: Tuple[int, ...]) -> torch.Tensor:
+    if not torch.is_tensor(t):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if tuple(t.shape) != shape:
+        raise ValueError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _problem(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, out, topk_idx=None,
+             topk_w=None) -> _lib.Problem:
+    p = _lib.Problem()
+    p.T, p.E_local, p.local_expert_offset, p.routed_scaling_factor = T, E_local, offset, scale
+    p.routing_logits = logits.data_ptr() if logits is not None else None
+    p.routing_bias = bias.data_ptr() if bias is not None else None
+    p.hidden_states = hs.data_ptr()
+    p.hidden_states_scale = hs_scale.data_ptr()
+    p.gemm1_weights = w13.data_ptr()
+    p.gemm1_weights_scale = w13s.data_ptr()
+    p.gemm2_weights = w2.data_ptr()
+    p.gemm2_weights_scale = w2s.data_ptr()
+    p.output = out.data_ptr()
+    p.topk_idx_in = topk_idx.data_ptr() if topk_idx is not None else None
+    p.topk_w_in = topk_w.data_ptr() if topk_w is not None else None
+    return p
+
+
+def _check_weights(hidden_states, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale):
+    if not torch.is_tensor(gemm1_weights) or gemm1_weights.dim() != 3:
+        raise ValueError("gemm1_weights must be [E_local, 4096, 7168]")
+    E_local = int(gemm1_weights.shape[0])
+    if not 1 <= E_local <= E_GLOBAL:
+        raise ValueError(f"E_local must be in 1..{E_GLOBAL}, got {E_local}")
+    w13 = _require(gemm1_weights, "gemm1_weights", _FP8, (E_local, 2 * I, H))
+    w13s = _require(gemm1_weights_scale, "gemm1_weights_scale", torch.float32, (E_local, 2 * I_BLOCKS, H_BLOCKS))
+    w2 = _require(gemm2_weights, "gemm2_weights", _FP8, (E_local, H, I))
+    w2s = _require(gemm2_weights_scale, "gemm2_weights_scale", torch.float32, (E_local, H_BLOCKS, I_BLOCKS))
+    return E_local, w13, w13s, w2, w2s
+
+
+def _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, topk_idx, topk_w):
+    device = hs.device
+    if offset < 0 or offset + E_local > E_GLOBAL:
+        raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")
+    if output is None:
+        output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+    else:
+        if output.dtype != torch.bfloat16 or tuple(output.shape) != (T, H) or not output.is_contiguous():
+            raise ValueError("output must be a contiguous bfloat16 tensor of shape [T, 7168]")
+        if output.device != device:
+            raise RuntimeError("output must live on the device of hidden_states")
+    if T == 0:
+        return output
+    with torch.cuda.device(device):
+        stream_ptr = torch.cuda.current_stream(device).cuda_stream
+        ws = _workspace(device, T, E_local, stream_ptr)
+        p = _problem(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, topk_idx,
+                     topk_w)
+        _lib.check(_lib.load().b200moe_forward(C.byref(p), C.byref(ws.struct), stream_ptr), "b200moe_forward")
+        if os.environ.get("B200MOE_CHECK_STATUS") == "1":
+            check_status(device)
+    return output
+
+
+@torch.no_grad()
+def kernel(
+    routing_logits,
+    routing_bias,
+    hidden_states,
+    hidden_states_scale,
+    gemm1_weights,
+    gemm1_weights_scale,
+    gemm2_weights,
+    gemm2_weights_scale,
+    local_expert_offset,
+    routed_scaling_factor,
+    output=None,
+):
+    """Fused MoE layer; same arguments as the reference ``kernel`` (solution/python/kernel.py:71-83).
+
+    routing_logits [T,256] f32 · routing_bias [256] bf16 · hidden_states [T,7168] e4m3 · hidden_states_scale [56,T] f32 ·
+    gemm1_weights [E,4096,7168] e4m3 · gemm1_weights_scale [E,32,56] f32 · gemm2_weights [E,7168,2048] e4m3 ·
+    gemm2_weights_scale [E,56,16] f32 · local_expert_offset, routed_scaling_factor: Python scalars or 0-d tensors ·
+    output: optional bf16 [T,7168] destination.  Returns the output tensor.  E (local experts) is taken from the weight
+    shape; the reference fixes it at 32.  Raises TypeError / ValueError on wrong dtypes or shapes and RuntimeError when
+    the CUDA library is missing, an input is not on a CUDA device, or a launch fails.
+    """
+    if not torch.is_tensor(routing_logits) or routing_logits.dim() != 2:
+        raise ValueError("routing_logits must be [T, 256]")
+    T = int(routing_logits.shape[0])
+    E_local, w13, w13s, w2, w2s = _check_weights(hidden_states, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                                                 gemm2_weights_scale)
+    logits = _require(routing_logits, "routing_logits", torch.float32, (T, E_GLOBAL))
+    bias = _require(routing_bias.reshape(-1) if torch.is_tensor(routing_bias) else routing_bias, "routing_bias",
+                    torch.bfloat16, (E_GLOBAL,))
+    hs = _require(hidden_states, "hidden_states", _FP8, (T, H))
+    hs_scale = _require(hidden_states_scale, "hidden_states_scale", torch.float32, (H_BLOCKS, T))
+    offset = _host_scalar(local_expert_offset, int)
+    scale = _host_scalar(routed_scaling_factor, float)
+    return _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, None, None)
+
+
+@torch.no_grad()
+def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                     gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None):
+    """Same layer for tokens whose routing already ran (expert-parallel receiver): ``topk_idx`` [T,8] int32 global
+    expert ids and ``topk_weights`` [T,8] f32 final weights replace logits, bias and scaling factor.  Only pairs whose
+    expert lies in [offset, offset+E) contribute.  The reference has no such entry (single GPU only)."""
+    if not torch.is_tensor(topk_idx) or topk_idx.dim() != 2:
+        raise ValueError("topk_idx must be [T, 8]")
+    T = int(topk_idx.shape[0])
+    E_local, w13, w13s, w2, w2s = _check_weights(hidden_states, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                                                 gemm2_weights_scale)
+    idx = _require(topk_idx, "topk_idx", torch.int32, (T, TOP_K))
+    w = _require(topk_weights, "topk_weights", torch.float32, (T, TOP_K))
+    hs = _require(hidden_states, "hidden_states", _FP8, (T, H))
+    hs_scale = _require(hidden_states_scale, "hidden_states_scale", torch.float32, (H_BLOCKS, T))
+    offset = _host_scalar(local_expert_offset, int)
+    return _run(T, E_local, offset, 1.0, None, None, hs, hs_scale, w13, w13s, w2, w2s, output, idx, w)
+
+
+def check_status(device=None) -> None:
+    """Synchronises the current stream and raises RuntimeError if any kernel since the last check recorded a failure
+    (a bounded device-side wait that ran out).  The reference has no device-side waits and no such check."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _devices.get(device.index)
+    if st is None or st.active is None:
+        return
+    ws = st.carved[st.active]
+    out = (C.c_int32 * 4)()
+    with torch.cuda.device(device):
+        rc = _lib.load().b200moe_read_status(C.byref(ws.struct), torch.cuda.current_stream(device).cuda_stream,
+                                             C.byref(out))
+    if rc == _lib.EDEVICE:
+        raise RuntimeError(f"device status word: code={out[0]} block={out[1]} role={out[2]} detail={out[3]}")
+    _lib.check(rc, "b200moe_read_status")
+
+
+def last_workspace(device=None) -> Optional[_Workspace]:
+    """The workspace view used by the most recent call on ``device`` (tests read the sort metadata through it)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _devices.get(device.index)
+    if st is None or st.active is None:
+        return None
+    return st.carved[st.active]

@@ -1,0 +1,173 @@
+/*
+ * b200moe.h — C ABI of libb200moe.so: the DeepSeek-V3 FP8 block-scale fused MoE layer for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the device side of the reference operator
+ *     kernel(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+ *            gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output)
+ * (reference: solution/python/kernel.py:71-83, host orchestration solution/python/pure_triton_impl.py:2125-2403).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - every function returns 0 (B200MOE_OK) or a negative B200MOE_E* code; nothing throws, exits or prints;
+ *   - no function synchronises the stream except b200moe_read_status();
+ *   - no function allocates device memory: the caller owns a workspace sized by b200moe_workspace_bytes().
+ *
+ * Fixed operator geometry (reference: solution/python/pure_triton_impl.py:23-57, solution/cuda/binding.py:24-31):
+ *   hidden H = 7168, intermediate I = 2048, 256 global experts in 8 groups of 32, top-4 groups, top-8 experts,
+ *   quantisation block 128.  The number of local experts E_local is a run-time argument (1..256); the reference
+ *   hard-codes 32.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_HIDDEN 7168
+#define B200MOE_INTER 2048
+#define B200MOE_NUM_EXPERTS 256
+#define B200MOE_TOP_K 8
+#define B200MOE_N_GROUP 8
+#define B200MOE_TOPK_GROUP 4
+#define B200MOE_QBLOCK 128
+#define B200MOE_BLOCK_M 128 /* rows per expert tile; every expert segment is padded to a multiple of this */
+
+enum {
+  B200MOE_OK = 0,
+  B200MOE_EINVAL = -1,    /* bad argument (null pointer, T < 0, E_local out of range, misaligned pointer) */
+  B200MOE_EWORKSPACE = -2,/* workspace too small or misaligned */
+  B200MOE_ECUDA = -3,     /* a CUDA runtime / driver call failed; see b200moe_last_cuda_error() */
+  B200MOE_EDEVICE = -4,   /* a kernel recorded a failure in the device status word (bounded wait ran out) */
+  B200MOE_EUNSUPPORTED = -5 /* the current device is not sm_100 */
+};
+
+/* Inputs and output of one layer call.  Tensor layouts are exactly those of the reference operator
+ * (solution/python/pure_triton_impl.py:2127-2137):
+ *   routing_logits        [T, 256]            float32, row-major
+ *   routing_bias          [256]               bfloat16
+ *   hidden_states         [T, 7168]           float8 e4m3fn
+ *   hidden_states_scale   [56, T]             float32 (k-block major: the 56 scales of one token are strided by T)
+ *   gemm1_weights         [E_local, 4096, 7168] e4m3fn  (rows 0..2047 = W1 "up", rows 2048..4095 = W3 "gate")
+ *   gemm1_weights_scale   [E_local, 32, 56]   float32
+ *   gemm2_weights         [E_local, 7168, 2048] e4m3fn
+ *   gemm2_weights_scale   [E_local, 56, 16]   float32
+ *   output                [T, 7168]           bfloat16; every row is written (zeros for tokens with no local expert)
+ *
+ * If routing_logits is NULL the routing stage is skipped and (topk_idx_in, topk_w_in) — [T,8] int32 global expert
+ * ids and [T,8] float32 final weights — are used instead.  This is the path the expert-parallel receiver takes for
+ * tokens routed on another rank; the reference has no counterpart (it only has `local_expert_offset`,
+ * solution/python/pure_triton_impl.py:2141). */
+typedef struct b200moe_problem {
+  int32_t T;
+  int32_t E_local;
+  int32_t local_expert_offset;
+  float routed_scaling_factor;
+  const float* routing_logits;
+  const uint16_t* routing_bias;
+  const uint8_t* hidden_states;
+  const float* hidden_states_scale;
+  const uint8_t* gemm1_weights;
+  const float* gemm1_weights_scale;
+  const uint8_t* gemm2_weights;
+  const float* gemm2_weights_scale;
+  uint16_t* output;
+  const int32_t* topk_idx_in;
+  const float* topk_w_in;
+} b200moe_problem;
+
+/* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
+ * Integer metadata follows the reference's sort kernel (solution/python/pure_triton_impl.py:474-551):
+ *   sorted_token_ids[r] = token of sorted row r, or T for a pad row;  sorted_weights[r] = routing weight or 0;
+ *   scatter_map[t*8+k]  = sorted row of pair (t,k), or -1 when expert k of token t is not local;
+ *   block_offsets[e]    = first 128-row block of local expert e, block_offsets[E_local] = total blocks.
+ * Within an expert, rows are in ascending token order (the order of a stable sort of the flat pair list by expert,
+ * as in solution/cuda/binding.py:147); the reference's Triton sort is atomic-ordered and not deterministic. */
+typedef struct b200moe_workspace {
+  int32_t T;
+  int32_t E_local;
+  int32_t R_max;
+  int32_t n_chunks;          /* ceil(T/32): tokens are ranked in chunks of one warp */
+  int32_t* topk_idx;         /* [T,8]   global expert ids, descending biased score, ties to the lower id */
+  float* topk_w;             /* [T,8]   s_k / (sum_k s_k + 1e-20) * routed_scaling_factor */
+  uint32_t* chunk_bits;      /* [n_chunks, E_local] bit j set: token 32*chunk+j selected local expert e */
+  int32_t* chunk_base;       /* [n_chunks, E_local] pairs of expert e in earlier chunks */
+  int32_t* counts;           /* [E_local] */
+  int32_t* block_offsets;    /* [E_local+1] */
+  int32_t* total_blocks;     /* [1] */
+  int32_t* status;           /* [4] device status word: 0 = ok */
+  int32_t* sorted_token_ids; /* [R_max] */
+  float* sorted_weights;     /* [R_max] */
+  int32_t* scatter_map;      /* [T*8] */
+  uint8_t* a_sorted;         /* [R_max, 7168] e4m3 activations gathered in sorted order */
+  float* a_scale_sorted;     /* [56, R_max]   their scales, k-block major */
+  uint8_t* inter_q;          /* [2, R_max, 2048] e4m3: SwiGLU output as value term + residual term, shared scale */
+  float* inter_scale;        /* [16, R_max]   per row per 128 columns */
+  uint16_t* expert_out;      /* [R_max, 7168] bf16 GEMM2 result per sorted row (unweighted) */
+} b200moe_workspace;
+
+/* Library / build identification.  No reference counterpart. */
+int b200moe_version(void);
+const char* b200moe_strerror(int code);
+/* Text of the last CUDA error seen by this thread ("" if none).  No reference counterpart. */
+const char* b200moe_last_cuda_error(void);
+
+/* Bytes of workspace needed for up to T tokens and E_local local experts.
+ * Replaces the reference's per-T module-level buffer caches (solution/python/pure_triton_impl.py:1945-1950,
+ * :2162-2205; MAX_PADDED = 8*T + 32*BLOCK_M at :2171). */
+int b200moe_workspace_bytes(int32_t T, int32_t E_local, size_t* bytes /* host */);
+
+/* Carve `base` (256-byte aligned, `bytes` long) into the typed view for exactly (T, E_local). */
+int b200moe_workspace_carve(void* base, size_t bytes, int32_t T, int32_t E_local, b200moe_workspace* out /* host */);
+
+/* Clears the device status word of a freshly carved workspace (asynchronous on `stream`); call once before the first
+ * launch that uses the workspace.  No reference counterpart. */
+int b200moe_workspace_init(const b200moe_workspace* ws /* host */, void* stream);
+
+/* Whole layer: route -> rank -> scatter -> gather -> GEMM1+SwiGLU -> GEMM2 -> weighted reduce, all on `stream`,
+ * no host synchronisation.  Replaces solution/python/pure_triton_impl.py:2125-2403 (kernel), :2025-2123 (_kernel_t1),
+ * solution/python/triton_impl.py:346-566 and solution/python/triton_impl_t901.py:40-185. */
+int b200moe_forward(const b200moe_problem* p /* host */, const b200moe_workspace* ws /* host */, void* stream);
+
+/* Stage entry points (unit tests, profiling).  Each runs one stage of b200moe_forward on the same buffers. */
+
+/* No-aux routing: sigmoid, +bias, group score = two largest of each 32-expert group, top-4 groups, top-8 experts,
+ * normalise, scale; also records which local experts each 32-token chunk selected (chunk_bits).
+ * Replaces triton_ds_routing_kernel / _fused_routing_histogram_kernel (solution/python/pure_triton_impl.py:96-265). */
+int b200moe_route(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* chunk_bits from an existing topk_idx (used when routing ran elsewhere).  No reference counterpart. */
+int b200moe_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* Per-expert prefix over chunks (chunk_base, counts), then the padded layout and the stable scatter
+ * (block_offsets, total_blocks, sorted_token_ids, sorted_weights, scatter_map).
+ * Replaces triton_sort_and_scatter_kernel and token_sort_and_scatter
+ * (solution/python/pure_triton_impl.py:474-551, :832-879). */
+int b200moe_sort(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* a_sorted / a_scale_sorted from hidden_states / hidden_states_scale via sorted_token_ids.
+ * Replaces the in-kernel row gather of the reference GEMM1 (solution/python/pure_triton_impl.py:986-994) and
+ * _dequantize_gemm1_sorted_a_kernel (solution/python/triton_impl.py:67-110), without the dequantisation. */
+int b200moe_gather(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* Grouped FP8 GEMM1 with fp32 block-scale promotion every 128 K, SwiGLU, two-term e4m3 re-quantisation.
+ * Replaces _fused_moe_gemm1_swiglu_kernel (solution/python/pure_triton_impl.py:886-1046) and the CuTe GEMM1 chain
+ * (solution/python/cute_gemm1_mma.py:247-289, solution/python/triton_impl.py:113-150). */
+int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* Grouped FP8 GEMM2 over the two-term intermediate, bf16 rows out.
+ * Replaces _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196) and the CuTe GEMM2
+ * (solution/python/cute_gemm2_mma.py:250-304). */
+int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* out[t] = sum_k topk_w[t,k] * expert_out[scatter_map[t,k]], fp32 accumulate, bf16 store, no atomics.
+ * Replaces _token_reduce_kernel (solution/python/pure_triton_impl.py:1758-1821) and
+ * _token_reduce_weighted_kernel (solution/python/triton_impl.py:163-207). */
+int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+
+/* Synchronises `stream`, copies the device status word to *status (host) and clears it.
+ * Returns B200MOE_EDEVICE if it was non-zero.  No reference counterpart (the reference has no device-side waits). */
+int b200moe_read_status(const b200moe_workspace* ws, void* stream, int32_t status[4] /* host */);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,62 @@
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
+
+# Acceptance bound on the bf16 output, per element, against the fp32-dequant oracle: |x - y| <= ATOL + RTOL * |y|.
+ATOL = 1e-2
+RTOL = 2e-2
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+def load_golden(name):
+    d = np.load(GOLDEN_DIR / f"{name}.npz")
+    T, E_local, offset, seed, skew, full = (int(x) for x in d["meta"])
+    rec = dict(T=T, E_local=E_local, offset=offset, seed=seed, skew=bool(skew), full=bool(full),
+               topk_idx=d["topk_idx"].astype(np.int64), topk_w=d["topk_w"])
+    if full:
+        rec["out_f32"] = d["out_f32"]
+        rec["hit_experts"] = d["hit_experts"].astype(np.int64).tolist()
+    return rec
+
+
+def golden_names(full=None):
+    names = sorted(p.stem for p in GOLDEN_DIR.glob("*.npz"))
+    if full is None:
+        return names
+    return [n for n in names if bool(np.load(GOLDEN_DIR / f"{n}.npz")["meta"][5]) == full]
+
+
+def assert_close(actual, expected, atol=ATOL, rtol=RTOL, what="output"):
+    """actual, expected: float arrays / tensors of the same shape."""
+    import torch
+    a = torch.as_tensor(actual).float()
+    e = torch.as_tensor(expected).float()
+    assert a.shape == e.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(e.shape)}"
+    assert torch.isfinite(a).all(), f"{what}: non-finite values"
+    err = (a - e).abs()
+    tol = atol + rtol * e.abs()
+    bad = err > tol
+    if bad.any():
+        worst = (err / tol).max().item()
+        raise AssertionError(f"{what}: {int(bad.sum())} of {a.numel()} elements out of tolerance; "
+                             f"max err/tol = {worst:.3f}, max abs err = {err.max().item():.4e}")
+    return (err / tol).max().item()
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle as oracle_mod
+    oracle_mod.build()
+    return oracle_mod

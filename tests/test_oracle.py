@@ -1,0 +1,80 @@
+"""CPU: the oracle (oracle/) against the golden outputs of the reference's own PyTorch path (tests/golden)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden_names, load_golden
+from fused_moe_b200 import synth
+
+
+def _sorted_by_expert(idx, w):
+    order = idx.argsort(dim=1)
+    return torch.gather(idx, 1, order), torch.gather(w, 1, order)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_routing_matches_reference(oracle, name):
+    g = load_golden(name)
+    inp = synth.make_inputs(g["T"], g["E_local"], seed=g["seed"], local_expert_offset=g["offset"], skew=g["skew"],
+                            only_experts=[])
+    idx, w = oracle.route(inp["routing_logits"], inp["routing_bias"], inp["routed_scaling_factor"])
+    # every token's eight experts are distinct and come in descending biased score, ties to the lower id
+    s = torch.sigmoid(inp["routing_logits"]) + inp["routing_bias"].float()
+    picked = torch.gather(s, 1, idx.long())
+    assert (picked[:, :-1] >= picked[:, 1:] - 1e-6).all()
+    sidx, sw = _sorted_by_expert(idx.long(), w)
+    assert (sidx[:, 1:] > sidx[:, :-1]).all()
+    # the expert SET per token is exactly the reference's (torch.topk leaves the order unspecified)
+    assert np.array_equal(sidx.numpy(), g["topk_idx"]), "expert sets differ from the reference"
+    np.testing.assert_allclose(sw.numpy(), g["topk_w"], rtol=2e-6, atol=1e-7)
+    np.testing.assert_allclose(w.sum(dim=1).numpy(), inp["routed_scaling_factor"], rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", golden_names(full=True))
+def test_forward_matches_reference(oracle, name):
+    g = load_golden(name)
+    inp = synth.make_inputs(g["T"], g["E_local"], seed=g["seed"], local_expert_offset=g["offset"], skew=g["skew"],
+                            only_experts=g["hit_experts"])
+    res = oracle.kernel(inp["routing_logits"], inp["routing_bias"], inp["hidden_states"], inp["hidden_states_scale"],
+                        inp["gemm1_weights"], inp["gemm1_weights_scale"], inp["gemm2_weights"],
+                        inp["gemm2_weights_scale"], inp["local_expert_offset"], inp["routed_scaling_factor"])
+    ref = torch.from_numpy(g["out_f32"])
+    # float32 sums in a different order: agree to float32 rounding, far inside the acceptance bound
+    assert_close(res["out_f32"], ref, atol=2e-5, rtol=2e-5, what=f"{name} fp32")
+    # and the bf16 rounding is the reference's cast (binding.py:185): equal up to a neighbouring bf16 value
+    assert_close(res["out_bf16"].float(), ref.bfloat16().float(), atol=1e-6, rtol=1.6e-2, what=f"{name} bf16")
+    if not g["hit_experts"]:
+        assert res["pairs"] == 0 and not res["out_f32"].any()
+
+
+def test_sigmoid_close_to_torch(oracle):
+    x = np.concatenate([np.linspace(-30, 30, 4001), [-100.0, 100.0, 0.0, -87.5, 88.5]]).astype(np.float32)
+    ours = oracle.sigmoid(x)
+    ref = torch.sigmoid(torch.from_numpy(x)).numpy()
+    np.testing.assert_allclose(ours, ref, rtol=4e-7, atol=1e-37)
+
+
+def test_sort_properties(oracle):
+    T, E, off = 300, 32, 64
+    inp = synth.make_inputs(T, E, seed=4, local_expert_offset=off, skew=True, only_experts=[])
+    idx, w = oracle.route(inp["routing_logits"], inp["routing_bias"], 2.5)
+    s = oracle.sort(idx, w, E, off)
+    counts, offs = s["counts"].numpy(), s["block_offsets"].numpy()
+    local = (idx >= off) & (idx < off + E)
+    assert counts.sum() == int(local.sum())
+    assert np.array_equal(offs[1:] - offs[:-1], (counts + 127) // 128)
+    ids, smap = s["sorted_token_ids"].numpy(), s["scatter_map"].numpy()
+    assert ((smap >= 0) == local.numpy()).all()
+    # stable order = the reference's argsort(stable=True) of the local pair list (binding.py:138-150)
+    flat_e = (idx.reshape(-1) - off)[local.reshape(-1)]
+    flat_t = torch.arange(T).repeat_interleave(8)[local.reshape(-1)]
+    order = flat_e.argsort(stable=True)
+    ref_tokens = flat_t[order].numpy()
+    got = np.concatenate([ids[offs[e] * 128: offs[e] * 128 + counts[e]] for e in range(E)])
+    assert np.array_equal(got, ref_tokens)
+    for e in range(E):
+        pad = ids[offs[e] * 128 + counts[e]: offs[e + 1] * 128]
+        assert (pad == T).all()
+    # scatter_map inverts the placement
+    for t, k in zip(*np.nonzero(smap >= 0)):
+        assert ids[smap[t, k]] == t and s["sorted_weights"][smap[t, k]] == w[t, k]
