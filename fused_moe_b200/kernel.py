@@ -105,9 +105,13 @@ def _require(t: torch.Tensor, name: str, dtype: torch.dtype, shape: Tuple[int, .
         raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
     if tuple(t.shape) != shape:
         raise ValueError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
-    if not t.is_cuda:
-        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
     return t if t.is_contiguous() else t.contiguous()
+
+
+def _require_cuda(**tensors) -> None:
+    for name, t in tensors.items():
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
 
 
 def _problem(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, out, topk_idx=None,
@@ -142,6 +146,9 @@ def _check_weights(hidden_states, gemm1_weights, gemm1_weights_scale, gemm2_weig
 
 
 def _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, topk_idx, topk_w):
+    _require_cuda(routing_logits=logits, routing_bias=bias, hidden_states=hs, hidden_states_scale=hs_scale,
+                  gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2, gemm2_weights_scale=w2s,
+                  topk_idx=topk_idx, topk_weights=topk_w)
     device = hs.device
     if offset < 0 or offset + E_local > E_GLOBAL:
         raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")

@@ -1,0 +1,206 @@
+"""GPU: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Integer results (expert ids, permutation, offsets) must be bit-exact; the bf16 output must satisfy
+|x - y| <= 1e-2 + 2e-2 |y| against the fp32-dequant oracle (tests/conftest.py: ATOL, RTOL).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+KEYS = ["routing_logits", "routing_bias", "hidden_states", "hidden_states_scale", "gemm1_weights",
+        "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale", "local_expert_offset", "routed_scaling_factor"]
+
+
+@pytest.fixture(scope="module")
+def moe():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fused_moe_b200 import kernel as k
+    from fused_moe_b200 import _lib
+    _lib.load()  # raises if libb200moe.so is missing: there is no fallback to test
+    return k
+
+
+_weights_cache = {}
+
+
+def gpu_inputs(T, E_local, seed, offset, skew):
+    from fused_moe_b200 import synth
+    key = (E_local, seed, offset)
+    w = _weights_cache.get(key)
+    if w is None:
+        _weights_cache.clear()
+    inp = synth.make_inputs(T, E_local, seed=seed, local_expert_offset=offset, skew=skew, device="cuda", weights=w)
+    _weights_cache[key] = inp
+    return inp
+
+
+def poison_workspace(moe, T, E_local):
+    """Fill the scratch buffer with 0xFF so that reads of rows the kernels never wrote show up as NaN / nonsense."""
+    from fused_moe_b200.kernel import _devices, workspace_bytes
+    st = _devices.get(torch.cuda.current_device())
+    if st is not None and st.buffer is not None:
+        st.buffer.fill_(0xFF)
+        st.active = None
+
+
+def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
+    inp = gpu_inputs(T, E_local, seed, offset, skew)
+    if poison:
+        moe.kernel(**inp)  # sizes the buffer
+        torch.cuda.synchronize()
+        poison_workspace(moe, T, E_local)
+    out = moe.kernel(**inp)
+    moe.check_status()
+    ws = moe.last_workspace()
+    assert out.shape == (T, 7168) and out.dtype == torch.bfloat16
+    ref = oracle.kernel(*[inp[k] for k in KEYS])
+
+    # routing: bit-exact ids (order included) and weights
+    idx = ws.view("topk_idx", torch.int32, (T, 8)).cpu()
+    w = ws.view("topk_w", torch.float32, (T, 8)).cpu()
+    assert torch.equal(idx, ref["topk_idx"]), "expert ids differ from the oracle"
+    assert torch.equal(w, ref["topk_w"]), "routing weights differ from the oracle"
+
+    # sort metadata: bit-exact
+    s = oracle.sort(ref["topk_idx"], ref["topk_w"], E_local, offset)
+    tb = int(ws.view("total_blocks", torch.int32, (1,)).item())
+    assert tb == s["total_blocks"]
+    assert torch.equal(ws.view("counts", torch.int32, (E_local,)).cpu(), s["counts"])
+    assert torch.equal(ws.view("block_offsets", torch.int32, (E_local + 1,)).cpu(), s["block_offsets"])
+    n = tb * 128
+    assert torch.equal(ws.view("sorted_token_ids", torch.int32, (ws.struct.R_max,))[:n].cpu(), s["sorted_token_ids"])
+    assert torch.equal(ws.view("sorted_weights", torch.float32, (ws.struct.R_max,))[:n].cpu(), s["sorted_weights"])
+    assert torch.equal(ws.view("scatter_map", torch.int32, (T, 8)).cpu(), s["scatter_map"])
+
+    ratio = assert_close(out.float().cpu(), ref["out_bf16"].float(), what=f"T={T} E={E_local} off={offset}")
+    return out, ref, ratio
+
+
+@pytest.mark.parametrize("T,E_local,seed,offset,skew", [
+    (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration
+    (1, 32, 5, 96, False),     # decode
+    (80, 32, 1, 0, False),     # small batch
+    (33, 8, 3, 60, False),     # E_local below one warp, non-zero offset, two token chunks
+    (40, 3, 13, 253, True),    # last experts, skewed router
+    (3, 2, 21, 100, False),    # no token reaches a local expert: all-zero output
+    (300, 32, 4, 64, True),    # an expert with more than one 128-row block
+])
+def test_layer_matches_oracle(moe, oracle, T, E_local, seed, offset, skew):
+    out, ref, _ = run_and_check(moe, oracle, T, E_local, seed, offset, skew)
+    if ref["pairs"] == 0:
+        assert not out.any()
+
+
+@pytest.mark.parametrize("name", golden_names(full=True))
+def test_layer_matches_reference_golden(moe, name):
+    """Straight against the reference's own outputs (tests/golden, made by solution/cuda/binding.py)."""
+    g = load_golden(name)
+    inp = gpu_inputs(g["T"], g["E_local"], g["seed"], g["offset"], g["skew"])
+    out = moe.kernel(**inp)
+    moe.check_status()
+    ws = moe.last_workspace()
+    idx = ws.view("topk_idx", torch.int32, (g["T"], 8)).cpu().long()
+    assert np.array_equal(idx.sort(dim=1).values.numpy(), g["topk_idx"])
+    assert_close(out.float().cpu(), torch.from_numpy(g["out_f32"]).bfloat16().float(), what=name)
+
+
+def test_routing_large_skewed(moe, oracle):
+    """Routing + sort alone at prefill size: bit-exact against the oracle, sets equal to the reference's torch code."""
+    from fused_moe_b200 import _lib, synth
+    from fused_moe_b200.kernel import _problem, _workspace
+    g = load_golden("route_t4096_skew")
+    T, E_local, off = g["T"], 32, 0
+    inp = synth.make_inputs(T, E_local, seed=g["seed"], skew=True, device="cuda", only_experts=[])
+    dev = torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = _workspace(dev, T, E_local, stream)
+    out = torch.empty((T, 7168), dtype=torch.bfloat16, device=dev)
+    p = _problem(T, E_local, off, 2.5, inp["routing_logits"], inp["routing_bias"], inp["hidden_states"],
+                 inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"], inp["gemm2_weights"],
+                 inp["gemm2_weights_scale"], out)
+    lib = _lib.load()
+    _lib.check(lib.b200moe_route(C.byref(p), C.byref(ws.struct), stream), "route")
+    _lib.check(lib.b200moe_sort(C.byref(p), C.byref(ws.struct), stream), "sort")
+    torch.cuda.synchronize()
+    idx = ws.view("topk_idx", torch.int32, (T, 8)).cpu()
+    w = ws.view("topk_w", torch.float32, (T, 8)).cpu()
+    ridx, rw = oracle.route(inp["routing_logits"], inp["routing_bias"], 2.5)
+    assert torch.equal(idx, ridx) and torch.equal(w, rw)
+    assert np.array_equal(idx.long().sort(dim=1).values.numpy(), g["topk_idx"])
+    s = oracle.sort(ridx, rw, E_local, off)
+    n = s["total_blocks"] * 128
+    assert torch.equal(ws.view("block_offsets", torch.int32, (E_local + 1,)).cpu(), s["block_offsets"])
+    assert torch.equal(ws.view("sorted_token_ids", torch.int32, (ws.struct.R_max,))[:n].cpu(), s["sorted_token_ids"])
+    assert torch.equal(ws.view("scatter_map", torch.int32, (T, 8)).cpu(), s["scatter_map"])
+    # chunk_bits from topk_idx alone (the expert-parallel receiver's path) equals the fused routing's
+    bits = ws.view("chunk_bits", torch.int32, (ws.struct.n_chunks, E_local)).clone()
+    ws.view("chunk_bits", torch.int32, (ws.struct.n_chunks, E_local)).fill_(-1)
+    p.routing_logits = None
+    p.topk_idx_in = ws.struct.topk_idx
+    p.topk_w_in = ws.struct.topk_w
+    _lib.check(lib.b200moe_topk_bits(C.byref(p), C.byref(ws.struct), stream), "topk_bits")
+    torch.cuda.synchronize()
+    assert torch.equal(ws.view("chunk_bits", torch.int32, (ws.struct.n_chunks, E_local)), bits)
+
+
+def test_from_topk_equals_routed(moe):
+    """kernel_from_topk with the routing's own (ids, weights) reproduces kernel() bit for bit."""
+    inp = gpu_inputs(80, 32, 1, 0, False)
+    out = moe.kernel(**inp).clone()
+    ws = moe.last_workspace()
+    idx = ws.view("topk_idx", torch.int32, (80, 8)).clone()
+    w = ws.view("topk_w", torch.float32, (80, 8)).clone()
+    out2 = moe.kernel_from_topk(idx, w, inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"],
+                                inp["gemm1_weights_scale"], inp["gemm2_weights"], inp["gemm2_weights_scale"], 0)
+    moe.check_status()
+    assert torch.equal(out, out2)
+
+
+def test_destination_passing_and_scalar_tensors(moe):
+    """output= is filled and returned; 0-d device tensors are accepted for the two scalars
+    (reference: solution/python/pure_triton_impl.py:2012-2020, scripts/diag_precision_modal.py:106-107)."""
+    inp = gpu_inputs(7, 32, 0, 0, False)
+    ref = moe.kernel(**inp).clone()
+    dst = torch.full((7, 7168), 3.0, dtype=torch.bfloat16, device="cuda")
+    args = dict(inp)
+    args["local_expert_offset"] = torch.tensor(0, dtype=torch.int32, device="cuda")
+    args["routed_scaling_factor"] = torch.tensor(2.5, dtype=torch.float32, device="cuda")
+    ret = moe.kernel(*[args[k] for k in KEYS], dst)
+    assert ret is dst and torch.equal(dst, ref)
+
+
+def test_argument_errors(moe):
+    inp = gpu_inputs(7, 32, 0, 0, False)
+    bad = dict(inp)
+    bad["routing_logits"] = inp["routing_logits"].double()
+    with pytest.raises(TypeError):
+        moe.kernel(**bad)
+    bad = dict(inp)
+    bad["hidden_states_scale"] = inp["hidden_states_scale"].t().contiguous()
+    with pytest.raises(ValueError):
+        moe.kernel(**bad)
+    bad = dict(inp)
+    bad["local_expert_offset"] = 250
+    with pytest.raises(ValueError):
+        moe.kernel(**bad)
+    bad = dict(inp)
+    bad["hidden_states"] = inp["hidden_states"].cpu()
+    with pytest.raises(RuntimeError):
+        moe.kernel(**bad)
+
+
+def test_empty_batch(moe):
+    inp = gpu_inputs(7, 32, 0, 0, False)
+    z = dict(inp)
+    z["routing_logits"] = inp["routing_logits"][:0]
+    z["hidden_states"] = inp["hidden_states"][:0]
+    z["hidden_states_scale"] = inp["hidden_states_scale"][:, :0].contiguous()
+    out = moe.kernel(**z)
+    assert out.shape == (0, 7168)

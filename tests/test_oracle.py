@@ -42,7 +42,7 @@ def test_forward_matches_reference(oracle, name):
     # float32 sums in a different order: agree to float32 rounding, far inside the acceptance bound
     assert_close(res["out_f32"], ref, atol=2e-5, rtol=2e-5, what=f"{name} fp32")
     # and the bf16 rounding is the reference's cast (binding.py:185): equal up to a neighbouring bf16 value
-    assert_close(res["out_bf16"].float(), ref.bfloat16().float(), atol=1e-6, rtol=1.6e-2, what=f"{name} bf16")
+    assert_close(res["out_bf16"].float(), ref.bfloat16().float(), atol=3e-5, rtol=1.6e-2, what=f"{name} bf16")
     if not g["hit_experts"]:
         assert res["pairs"] == 0 and not res["out_f32"].any()
 
