@@ -1,0 +1,152 @@
+"""Expert-parallel sharding of the 256 experts over G ranks (one process per GPU, torch.distributed).
+
+The reference is single-GPU: its only hook for sharding is ``local_expert_offset``
+(solution/python/pure_triton_impl.py:2141, masks at :248 and :505).  This module adds what a G-GPU deployment needs:
+
+  rank r owns global experts [r*E_l, (r+1)*E_l), E_l = 256/G, and a slice of the tokens;
+  1. every rank routes ITS tokens (all 256 logits are per token, the bias is replicated);
+  2. dispatch: a token row (7168 e4m3 bytes + 56 scales + its 8 expert ids + 8 weights = 7456 bytes) goes once to
+     every rank that owns at least one of its experts — group-limited routing bounds that by 4 ranks at G = 8;
+  3. the receiver runs the layer on what arrived (``kernel_from_topk``: sort, gather, GEMM1+SwiGLU, GEMM2, reduce over
+     ITS experts only), giving one partial row per received token, already weighted and summed over its experts;
+  4. combine: partial rows return to the token's home rank, which adds them in fp32 and rounds to bf16.
+
+Collectives are two ``all_to_all_single`` per direction (split sizes, then payload) over NCCL (NVLink/NVSwitch); payloads
+land in local HBM before any kernel reads them.  Routing and the expert path are injected callables, so the same
+plumbing runs on CPU ranks (gloo) in the tests with the CPU oracle standing in for the CUDA library.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+H = 7168
+H_BLOCKS = 56
+TOP_K = 8
+E_GLOBAL = 256
+ROW_BYTES = H + 4 * H_BLOCKS + 4 * TOP_K + 4 * TOP_K  # 7456, a multiple of 16
+
+
+@dataclass
+class DispatchPlan:
+    """Who sends what: built on the home rank from its tokens' expert ids."""
+
+    send_token: torch.Tensor      # [n_send] local token id of each outgoing row, grouped by destination rank
+    send_splits: list             # rows per destination rank
+    recv_splits: list             # rows per source rank
+
+
+def plan_dispatch(topk_idx: torch.Tensor, world: int, group=None) -> DispatchPlan:
+    """topk_idx [T,8] global expert ids -> rows to send, ordered by destination rank then token id.  The split sizes
+    are exchanged with one small all_to_all and read back to the host (the collective needs them there)."""
+    e_per_rank = E_GLOBAL // world
+    T = topk_idx.shape[0]
+    dest = topk_idx.long() // e_per_rank                                   # [T,8]
+    hit = torch.zeros((T, world), dtype=torch.bool, device=topk_idx.device)
+    hit.scatter_(1, dest, True)
+    # nonzero of the transposed mask enumerates (rank, token) pairs rank-major with ascending token ids
+    pairs = hit.t().nonzero(as_tuple=False)
+    send_token = pairs[:, 1].contiguous()
+    send_counts = hit.sum(dim=0).to(torch.int64)
+    recv_counts = torch.empty_like(send_counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts.copy_(send_counts)
+    both = torch.stack([send_counts, recv_counts]).cpu()
+    return DispatchPlan(send_token=send_token, send_splits=both[0].tolist(), recv_splits=both[1].tolist())
+
+
+def pack_rows(tokens: torch.Tensor, hidden_states: torch.Tensor, hidden_states_scale: torch.Tensor,
+              topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+    """-> uint8 [n, 7456]: e4m3 row | 56 fp32 scales | 8 int32 expert ids | 8 fp32 weights, for the given tokens."""
+    n = tokens.shape[0]
+    buf = torch.empty((n, ROW_BYTES), dtype=torch.uint8, device=hidden_states.device)
+    hs_u8 = hidden_states.view(torch.uint8)
+    buf[:, :H] = hs_u8.index_select(0, tokens)
+    scales = hidden_states_scale.t().index_select(0, tokens).contiguous()  # [n,56]
+    buf[:, H:H + 224] = scales.view(torch.uint8).view(n, 224)
+    buf[:, H + 224:H + 256] = topk_idx.to(torch.int32).index_select(0, tokens).contiguous().view(torch.uint8).view(n, 32)
+    buf[:, H + 256:] = topk_w.index_select(0, tokens).contiguous().view(torch.uint8).view(n, 32)
+    return buf
+
+
+def unpack_rows(buf: torch.Tensor):
+    """Inverse of pack_rows -> (hidden e4m3 [n,7168], scales [56,n] fp32, topk_idx [n,8] int32, topk_w [n,8] fp32)."""
+    n = buf.shape[0]
+    hs = buf[:, :H].contiguous().view(torch.float8_e4m3fn)
+    scales = buf[:, H:H + 224].contiguous().view(torch.float32).view(n, H_BLOCKS).t().contiguous()
+    idx = buf[:, H + 224:H + 256].contiguous().view(torch.int32).view(n, TOP_K)
+    w = buf[:, H + 256:].contiguous().view(torch.float32).view(n, TOP_K)
+    return hs, scales, idx, w
+
+
+def _a2a(send: torch.Tensor, send_splits, recv_splits, world: int, group) -> torch.Tensor:
+    recv = torch.empty((sum(recv_splits),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    if world > 1:
+        dist.all_to_all_single(recv, send, output_split_sizes=recv_splits, input_split_sizes=send_splits, group=group)
+    else:
+        recv.copy_(send)
+    return recv
+
+
+class ExpertParallelMoE:
+    """One rank's shard of the layer.
+
+    route_fn(logits [T,256], bias [256], scale) -> (topk_idx int32 [T,8], topk_w fp32 [T,8])
+    expert_fn(topk_idx [n,8], topk_w [n,8], hidden e4m3 [n,7168], scales [56,n]) -> partial rows bf16 [n,7168]
+              (sum over THIS rank's experts of weight * expert output; zeros where none is local)
+    """
+
+    def __init__(self, route_fn: Callable, expert_fn: Callable, rank: int, world: int, group=None):
+        if E_GLOBAL % world:
+            raise ValueError(f"world size {world} does not divide {E_GLOBAL} experts")
+        self.route_fn, self.expert_fn = route_fn, expert_fn
+        self.rank, self.world, self.group = rank, world, group
+        self.e_local = E_GLOBAL // world
+        self.last_plan: Optional[DispatchPlan] = None
+        self.last_recv = None  # (topk_idx, topk_w, hidden, scales) of the rows this rank received last
+
+    @property
+    def local_expert_offset(self) -> int:
+        return self.rank * self.e_local
+
+    @torch.no_grad()
+    def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor,
+                output: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = routing_logits.shape[0]
+        topk_idx, topk_w = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
+        plan = plan_dispatch(topk_idx, self.world, self.group)
+        self.last_plan = plan
+        send = pack_rows(plan.send_token, hidden_states, hidden_states_scale, topk_idx, topk_w)
+        recv = _a2a(send, plan.send_splits, plan.recv_splits, self.world, self.group)
+        hs, scales, idx, w = unpack_rows(recv)
+        self.last_recv = (idx, w, hs, scales)
+        partial = self.expert_fn(idx, w, hs, scales)
+        back = _a2a(partial, plan.recv_splits, plan.send_splits, self.world, self.group)
+        acc = torch.zeros((T, H), dtype=torch.float32, device=hidden_states.device)
+        acc.index_add_(0, plan.send_token, back.float())
+        if output is None:
+            return acc.to(torch.bfloat16)
+        output.copy_(acc)
+        return output
+
+
+def make_cuda_shard(weights: dict, rank: int, world: int, group=None) -> ExpertParallelMoE:
+    """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts)."""
+    from . import kernel as K
+
+    e_local = E_GLOBAL // world
+    offset = rank * e_local
+
+    def route_fn(logits, bias, scale):
+        return K.route(logits, bias, scale)
+
+    def expert_fn(idx, w, hs, scales):
+        return K.kernel_from_topk(idx, w, hs, scales, weights["gemm1_weights"], weights["gemm1_weights_scale"],
+                                  weights["gemm2_weights"], weights["gemm2_weights_scale"], offset)
+
+    return ExpertParallelMoE(route_fn, expert_fn, rank, world, group)

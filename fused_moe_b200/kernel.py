@@ -229,6 +229,32 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
     return _run(T, E_local, offset, 1.0, None, None, hs, hs_scale, w13, w13s, w2, w2s, output, idx, w)
 
 
+@torch.no_grad()
+def route(routing_logits, routing_bias, routed_scaling_factor):
+    """Routing stage alone -> (topk_idx int32 [T,8], topk_weights float32 [T,8]); experts in descending biased score,
+    ties to the lower id (reference: solution/python/pure_triton_impl.py:96-190).  Used by expert-parallel ranks, which
+    route their own tokens before dispatch."""
+    if not torch.is_tensor(routing_logits) or routing_logits.dim() != 2:
+        raise ValueError("routing_logits must be [T, 256]")
+    T = int(routing_logits.shape[0])
+    logits = _require(routing_logits, "routing_logits", torch.float32, (T, E_GLOBAL))
+    bias = _require(routing_bias.reshape(-1), "routing_bias", torch.bfloat16, (E_GLOBAL,))
+    _require_cuda(routing_logits=logits, routing_bias=bias)
+    device = logits.device
+    if T == 0:
+        return (torch.empty((0, TOP_K), dtype=torch.int32, device=device),
+                torch.empty((0, TOP_K), dtype=torch.float32, device=device))
+    with torch.cuda.device(device):
+        stream_ptr = torch.cuda.current_stream(device).cuda_stream
+        ws = _workspace(device, T, 1, stream_ptr)
+        p = _lib.Problem()
+        p.T, p.E_local, p.local_expert_offset = T, 1, 0
+        p.routed_scaling_factor = _host_scalar(routed_scaling_factor, float)
+        p.routing_logits, p.routing_bias = logits.data_ptr(), bias.data_ptr()
+        _lib.check(_lib.load().b200moe_route(C.byref(p), C.byref(ws.struct), stream_ptr), "b200moe_route")
+        return ws.view("topk_idx", torch.int32, (T, TOP_K)).clone(), ws.view("topk_w", torch.float32, (T, TOP_K)).clone()
+
+
 def check_status(device=None) -> None:
     """Synchronises the current stream and raises RuntimeError if any kernel since the last check recorded a failure
     (a bounded device-side wait that ran out).  The reference has no device-side waits and no such check."""

@@ -204,3 +204,26 @@ def test_empty_batch(moe):
     z["hidden_states_scale"] = inp["hidden_states_scale"][:, :0].contiguous()
     out = moe.kernel(**z)
     assert out.shape == (0, 7168)
+
+
+def test_expert_parallel_shard_world1(moe):
+    """The expert-parallel plumbing with one rank (dispatch and combine are local copies) reproduces kernel()."""
+    from fused_moe_b200 import ep
+    inp = gpu_inputs(300, 32, 4, 64, True)
+    want = moe.kernel(**inp).clone()
+    full = dict(inp)
+    # a world-1 shard owns all 256 experts: embed the 32 generated experts at their global position
+    E = 256
+    w13 = torch.zeros((E, 4096, 7168), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    w13s = torch.zeros((E, 32, 56), dtype=torch.float32, device="cuda")
+    w2 = torch.zeros((E, 7168, 2048), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    w2s = torch.zeros((E, 56, 16), dtype=torch.float32, device="cuda")
+    w13[64:96], w13s[64:96], w2[64:96], w2s[64:96] = (inp["gemm1_weights"], inp["gemm1_weights_scale"],
+                                                      inp["gemm2_weights"], inp["gemm2_weights_scale"])
+    shard = ep.make_cuda_shard(dict(gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2,
+                                    gemm2_weights_scale=w2s), rank=0, world=1)
+    got = shard.forward(inp["routing_logits"], inp["routing_bias"], inp["hidden_states"], inp["hidden_states_scale"],
+                        inp["routed_scaling_factor"])
+    moe.check_status()
+    # experts outside 64..95 have zero weights and add nothing; the fp32 combine re-rounds to bf16
+    assert_close(got.float(), want.float(), atol=1e-6, rtol=1e-2, what="ep world 1")
