@@ -14,8 +14,9 @@
 // row.  MODE 1 uses two 128-row weight boxes per chunk (W1 rows n0.., W3 rows 2048+n0..) laid out back to back so a
 // single N=256 MMA produces both SwiGLU operands; MODE 2 uses one 256-row box of W2 and two A boxes (the two terms).
 //
-// Warp roles (320 threads): warps 0-7 promote TMEM partials into fp32 registers and run the epilogue (warp w owns TMEM
-// lanes 32*(w%4).. and half of the columns), warp 8 issues TMA loads, warp 9 owns TMEM and issues the MMAs.
+// Warp roles (384 threads): warps 0-7 promote TMEM partials into fp32 registers and run the epilogue (warp w owns TMEM
+// lanes 32*(w%4).. and half of the columns), warp 8 issues TMA loads, warp 9 owns TMEM and issues the MMAs, warps 10-11
+// only exist so that the third warpgroup can hand its registers to the other two (setmaxnreg 40 / 232).
 // fp32 block scales are not power-of-two, so the hardware block-scaled MMA cannot apply them: each 128-K chunk is
 // accumulated on its own into one of two 256-column TMEM stages and folded into registers with one FMA per element
 // while the next chunk's MMAs run into the other stage.
@@ -32,9 +33,13 @@ constexpr int TILE_N = 256;                    // TMEM columns per accumulator s
 constexpr int A_TILE_BYTES = BLOCK_M * 128;    // 16 KB
 constexpr int B_TILE_BYTES = TILE_N * 128;     // 32 KB
 constexpr int NUM_PROMO_WARPS = 8;
+#ifndef B200MOE_LDW
+#define B200MOE_LDW 32
+#endif
+constexpr int LDW = B200MOE_LDW;             // TMEM columns per tcgen05.ld of a promotion warp
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
-constexpr int GEMM_THREADS = 320;
+constexpr int GEMM_THREADS = 384;            // 3 warpgroups: 2 x promotion, 1 x {TMA, MMA, 2 idle warps}
 
 template <int MODE>
 struct Cfg {
@@ -159,6 +164,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int total_tiles = aux->off[E] * NT;
   volatile int* abort_flag = &aux->abort_flag;
 
+  // Each register budget is set inside the branch it governs, so the compiler sees one budget per region.
+  if (warp >= NUM_PROMO_WARPS) {
+  setmaxnreg_dec_aux();
   if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------------ TMA producer (lane 0 issues, warp stays converged)
     int stage = 0;
@@ -235,7 +243,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (acc == 0) acc_phase ^= 1u;
       }
     }
+  }
   } else {
+    setmaxnreg_inc_promo();
     // ------------------------------------------------------------------ promotion + epilogue (8 warps)
     const int q = warp & 3;       // TMEM lane quarter this warp may read
     const int h = warp >> 2;      // column half
@@ -278,21 +288,32 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * TILE_N) + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          // MODE 1: columns [64h,64h+64) hold W1 ("up"), [128+64h, 128+64h+64) hold W3 ("gate").
-          const int col = (MODE == 1) ? ((i >> 1) * 128 + h * 64 + (i & 1) * 32) : (h * 128 + i * 32);
-          const float sc = (MODE == 1 && i >= 2) ? sc1 : sc0;
-          uint32_t tmp[32];
-          tmem_ld32(taddr + static_cast<uint32_t>(col), tmp);
+        for (int i = 0; i < 128 / LDW; ++i) {
+          // this warp's 128 accumulators = two runs of 64 TMEM columns:
+          // MODE 1: [64h, 64h+64) holds W1 ("up"), [128+64h, 128+64h+64) holds W3 ("gate"); MODE 2: [128h, 128h+128).
+          const int run = (i * LDW) / 64, within = (i * LDW) % 64;
+          const int col = ((MODE == 1) ? (run * 128 + h * 64) : (h * 128 + run * 64)) + within;
+          const float sc = (MODE == 1 && run == 1) ? sc1 : sc0;
+          uint32_t tmp[LDW];
+#ifndef B200MOE_DIAG_NO_LD
+          tmem_ld(taddr + static_cast<uint32_t>(col), tmp);
           tc_wait_ld();
-          if (i == 3) {
+#else
+#pragma unroll
+          for (int j = 0; j < LDW; ++j) tmp[j] = __float_as_uint(sc);
+#endif
+          if (i == 128 / LDW - 1) {
             // all of this warp's reads of the stage are complete: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[acc]));
           }
+#ifndef B200MOE_DIAG_NO_FMA
 #pragma unroll
-          for (int j = 0; j < 32; ++j) accs[i * 32 + j] = fmaf(__uint_as_float(tmp[j]), sc, accs[i * 32 + j]);
+          for (int j = 0; j < LDW; ++j) accs[i * LDW + j] = fmaf(__uint_as_float(tmp[j]), sc, accs[i * LDW + j]);
+#else
+          accs[i * LDW] += __uint_as_float(tmp[0] ^ tmp[LDW - 1]);
+#endif
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;

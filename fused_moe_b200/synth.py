@@ -57,6 +57,9 @@ def _fields_sum(h: torch.Tensor) -> torch.Tensor:
 
 
 _INV_STD = 1.0 / 53509.6  # std of the sum of eight uniform{0..65535}
+# amax/448 written as a multiplication: torch divides by a scalar exactly on the CPU but multiplies by the reciprocal on
+# CUDA, which would make the two devices disagree in the last bit of the scale
+_INV_448 = 1.0 / 448.0
 
 
 def normal(n: int, seed: int, tag: int, sub: int = 0, device="cpu") -> torch.Tensor:
@@ -72,7 +75,7 @@ def quantize_act(x: torch.Tensor):
     """[T,7168] float32 -> (e4m3 [T,7168], scales [56,T] float32), one scale per token per 128 columns."""
     T = x.shape[0]
     xb = x.view(T, H // 128, 128)
-    s = (xb.abs().amax(dim=2) / 448.0).clamp_min(1e-12)
+    s = (xb.abs().amax(dim=2) * _INV_448).clamp_min(1e-12)
     q = (xb / s.unsqueeze(2)).to(_FP8).view(T, H)
     return q, s.t().contiguous()
 
@@ -81,7 +84,7 @@ def quantize_weight(w: torch.Tensor):
     """[N,K] float32 -> (e4m3 [N,K], scales [N/128, K/128] float32), one scale per 128x128 block."""
     N, K = w.shape
     wb = w.view(N // 128, 128, K // 128, 128)
-    s = (wb.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    s = (wb.abs().amax(dim=(1, 3)) * _INV_448).clamp_min(1e-12)
     q = (wb / s[:, None, :, None]).to(_FP8).view(N, K)
     return q, s.contiguous()
 

@@ -227,3 +227,16 @@ def test_expert_parallel_shard_world1(moe):
     moe.check_status()
     # experts outside 64..95 have zero weights and add nothing; the fp32 combine re-rounds to bf16
     assert_close(got.float(), want.float(), atol=1e-6, rtol=1e-2, what="ep world 1")
+
+
+def test_synth_cpu_and_cuda_generate_identical_bytes(moe):
+    """The golden fixtures were generated on a CPU; the GPU tests regenerate their inputs on the device."""
+    from fused_moe_b200 import synth
+    a = synth.make_inputs(5, 2, seed=9, local_expert_offset=10, skew=True, only_experts=[1], device="cpu")
+    b = synth.make_inputs(5, 2, seed=9, local_expert_offset=10, skew=True, only_experts=[1], device="cuda")
+    for k, v in a.items():
+        if torch.is_tensor(v):
+            x = v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v
+            y = b[k].cpu()
+            y = y.view(torch.uint8) if y.dtype == torch.float8_e4m3fn else y
+            assert torch.equal(x, y), k
