@@ -57,25 +57,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Wait on an mbarrier phase with a wall-clock limit.  Returns false (and records why) instead of hanging:
-// `abort_flag` is a CTA-shared word every waiting role polls, so one role giving up releases the others quickly.
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s; a healthy wait is microseconds
+// Wait on an mbarrier phase with a time limit.  Returns false (and records why) instead of hanging: `abort_flag` is a
+// CTA-shared word every waiting role polls, so one role giving up releases the others quickly.  The limit is counted
+// on the SM's cycle counter, read only once per 1024 polls, so a healthy wait (microseconds) never touches a timer.
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s at B200 clocks
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int role, int detail) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = global_timer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
         if (atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT) == ST_OK) {
           status[1] = static_cast<int>(blockIdx.x);
@@ -162,8 +159,7 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 }
 __device__ __forceinline__ void setmaxnreg_inc_promo() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 __device__ __forceinline__ void setmaxnreg_dec_aux() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
+
 
 // UMMA shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle
 // (8-row x 128-byte atoms, 1024 bytes apart).  Bits: [0,14) address>>4, [16,30) leading byte offset>>4 (unused for

@@ -33,10 +33,6 @@ constexpr int TILE_N = 256;                    // TMEM columns per accumulator s
 constexpr int A_TILE_BYTES = BLOCK_M * 128;    // 16 KB
 constexpr int B_TILE_BYTES = TILE_N * 128;     // 32 KB
 constexpr int NUM_PROMO_WARPS = 8;
-#ifndef B200MOE_LDW
-#define B200MOE_LDW 32
-#endif
-constexpr int LDW = B200MOE_LDW;             // TMEM columns per tcgen05.ld of a promotion warp
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
 constexpr int GEMM_THREADS = 384;            // 3 warpgroups: 2 x promotion, 1 x {TMA, MMA, 2 idle warps}
@@ -268,9 +264,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ws0_ptr = args.w_scale + (static_cast<size_t>(ti.e) * H_BLOCKS + ti.nt * 2 + h) * I_BLOCKS;
         ws1_ptr = ws0_ptr;
       }
-      float accs[128];
+      // 128 fp32 accumulators per thread, kept as 64 pairs so the promotion runs on the packed FMA (2 lanes / issue)
+      float2 acc2[64];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) accs[j] = 0.f;
+      for (int j = 0; j < 64; ++j) acc2[j] = make_float2(0.f, 0.f);
+#define ACC(j) (((j) & 1) ? acc2[(j) >> 1].y : acc2[(j) >> 1].x)
 
       float rs_n = __ldg(rs_ptr);
       float w0_n = __ldg(ws0_ptr);
@@ -287,33 +285,27 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * TILE_N) + (static_cast<uint32_t>(q * 32) << 16);
+        // This warp's 128 accumulators are two runs of 64 TMEM columns — MODE 1: [64h, 64h+64) holds W1 ("up") and
+        // [128+64h, 128+64h+64) holds W3 ("gate"); MODE 2: [128h, 128h+128) — each read with one 64-column load
+        // (fewer, wider loads measured faster than four 32-column loads, pipelined or not).
 #pragma unroll
-        for (int i = 0; i < 128 / LDW; ++i) {
-          // this warp's 128 accumulators = two runs of 64 TMEM columns:
-          // MODE 1: [64h, 64h+64) holds W1 ("up"), [128+64h, 128+64h+64) holds W3 ("gate"); MODE 2: [128h, 128h+128).
-          const int run = (i * LDW) / 64, within = (i * LDW) % 64;
-          const int col = ((MODE == 1) ? (run * 128 + h * 64) : (h * 128 + run * 64)) + within;
+        for (int run = 0; run < 2; ++run) {
+          const uint32_t col = static_cast<uint32_t>((MODE == 1) ? (run * 128 + h * 64) : (h * 128 + run * 64));
           const float sc = (MODE == 1 && run == 1) ? sc1 : sc0;
-          uint32_t tmp[LDW];
-#ifndef B200MOE_DIAG_NO_LD
-          tmem_ld(taddr + static_cast<uint32_t>(col), tmp);
+          uint32_t tmp[64];
+          tmem_ld64(taddr + col, tmp);
           tc_wait_ld();
-#else
-#pragma unroll
-          for (int j = 0; j < LDW; ++j) tmp[j] = __float_as_uint(sc);
-#endif
-          if (i == 128 / LDW - 1) {
+          if (run == 1) {
             // all of this warp's reads of the stage are complete: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[acc]));
           }
-#ifndef B200MOE_DIAG_NO_FMA
+          const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
-          for (int j = 0; j < LDW; ++j) accs[i * LDW + j] = fmaf(__uint_as_float(tmp[j]), sc, accs[i * LDW + j]);
-#else
-          accs[i * LDW] += __uint_as_float(tmp[0] ^ tmp[LDW - 1]);
-#endif
+          for (int j = 0; j < 32; ++j)
+            acc2[run * 32 + j] = __ffma2_rn(make_float2(__uint_as_float(tmp[2 * j]), __uint_as_float(tmp[2 * j + 1])),
+                                            sc2, acc2[run * 32 + j]);
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
@@ -321,12 +313,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!ok) break;
 
       if (MODE == 1) {
-        // accs[0..63] = up (W1) columns 64h.., accs[64..127] = gate (W3) for the same columns.
+        // accumulators 0..63 = up (W1) columns 64h.., 64..127 = gate (W3) for the same columns.
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
-          accs[j] = silu_mul(accs[64 + j], accs[j]);
-          amax = fmaxf(amax, fabsf(accs[j]));
+          ACC(j) = silu_mul(ACC(64 + j), ACC(j));
+          amax = fmaxf(amax, fabsf(ACC(j)));
         }
         float* ex = &aux->amax[tile_iter & 1][0][0];
         ex[h * BLOCK_M + r_in_tile] = amax;
@@ -348,11 +340,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const int j = v * 16 + u * 4;
-              w1[u] = pack4_e4m3(accs[j] * inv, accs[j + 1] * inv, accs[j + 2] * inv, accs[j + 3] * inv);
+              w1[u] = pack4_e4m3(ACC(j) * inv, ACC(j + 1) * inv, ACC(j + 2) * inv, ACC(j + 3) * inv);
               float back[4];
               unpack4_e4m3(w1[u], back);
-              w2[u] = pack4_e4m3((accs[j] - back[0] * s) * inv, (accs[j + 1] - back[1] * s) * inv,
-                                 (accs[j + 2] - back[2] * s) * inv, (accs[j + 3] - back[3] * s) * inv);
+              w2[u] = pack4_e4m3((ACC(j) - back[0] * s) * inv, (ACC(j + 1) - back[1] * s) * inv,
+                                 (ACC(j + 2) - back[2] * s) * inv, (ACC(j + 3) - back[3] * s) * inv);
             }
             reinterpret_cast<uint4*>(q1p)[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
             reinterpret_cast<uint4*>(q2p)[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
@@ -367,7 +359,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t o[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(accs[v * 8 + u * 2], accs[v * 8 + u * 2 + 1]);
+              __nv_bfloat162 b = __floats2bfloat162_rn(ACC(v * 8 + u * 2), ACC(v * 8 + u * 2 + 1));
               o[u] = *reinterpret_cast<uint32_t*>(&b);
             }
             reinterpret_cast<uint4*>(op)[v] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -377,6 +369,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
+#undef ACC
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
