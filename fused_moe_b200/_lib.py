@@ -33,6 +33,7 @@ class Problem(C.Structure):
         ("output", C.c_void_p),
         ("topk_idx_in", C.c_void_p),
         ("topk_w_in", C.c_void_p),
+        ("output_f32", C.c_void_p),
     ]
 
 

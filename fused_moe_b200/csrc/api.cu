@@ -77,7 +77,7 @@ static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
   uint8_t* a_scale_sorted = take(sizeof(float) * H_BLOCKS * R);
   uint8_t* inter_q = take(2 * R * I);
   uint8_t* inter_scale = take(sizeof(float) * I_BLOCKS * R);
-  uint8_t* expert_out = take(sizeof(uint16_t) * R * H);
+  uint8_t* expert_out = take(sizeof(float) * R * H);
   if (w) {
     w->T = T;
     w->E_local = E;
@@ -98,7 +98,7 @@ static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
     w->a_scale_sorted = reinterpret_cast<float*>(a_scale_sorted);
     w->inter_q = inter_q;
     w->inter_scale = reinterpret_cast<float*>(inter_scale);
-    w->expert_out = reinterpret_cast<uint16_t*>(expert_out);
+    w->expert_out = reinterpret_cast<float*>(expert_out);
   }
   return off;
 }
@@ -225,7 +225,8 @@ int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
-  if (p->T > 0 && (!p->output || !aligned16(p->output))) return B200MOE_EINVAL;
+  if (p->T > 0 && ((!p->output && !p->output_f32) || !aligned16(p->output) || !aligned16(p->output_f32)))
+    return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
   return launch_reduce(p, ws, static_cast<cudaStream_t>(stream));
@@ -236,10 +237,10 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   if (rc) return rc;
   if (p->T == 0) return B200MOE_OK;
   if (!p->hidden_states || !p->hidden_states_scale || !p->gemm1_weights || !p->gemm1_weights_scale ||
-      !p->gemm2_weights || !p->gemm2_weights_scale || !p->output)
+      !p->gemm2_weights || !p->gemm2_weights_scale || (!p->output && !p->output_f32))
     return B200MOE_EINVAL;
   if (!aligned16(p->hidden_states) || !aligned16(p->gemm1_weights) || !aligned16(p->gemm2_weights) ||
-      !aligned16(p->output))
+      !aligned16(p->output) || !aligned16(p->output_f32))
     return B200MOE_EINVAL;
   if (p->routing_logits) {
     if (!p->routing_bias) return B200MOE_EINVAL;

@@ -6,7 +6,8 @@
 //           Reference: _fused_moe_gemm1_swiglu_kernel (solution/python/pure_triton_impl.py:886-1046), oracle math
 //           solution/cuda/binding.py:166-175.
 //   MODE 2  GEMM2:  O = inter[R,2048] x W2[e]^T, both e4m3 terms accumulate into the same TMEM tile, promoted with
-//           inter_scale[row,kb] * w2_scale[e,nb,kb]; bf16 rows out.
+//           inter_scale[row,kb] * w2_scale[e,nb,kb]; float32 rows out (eight of them
+//           are later summed per token, so they are not rounded here).
 //           Reference: _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196), oracle math
 //           solution/cuda/binding.py:178-179.
 //
@@ -53,7 +54,7 @@ struct GemmArgs {
   const float* w_scale;      // MODE1: [E,32,56]; MODE2: [E,56,16]
   uint8_t* inter_q;          // MODE1 out: [2,R_max,2048]
   float* inter_scale;        // MODE1 out: [16,R_max]
-  uint16_t* expert_out;      // MODE2 out: [R_max,7168] bf16
+  float* expert_out;         // MODE2 out: [R_max,7168] float32
   int* status;
   int E_local;
   int R_max;
@@ -353,17 +354,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       } else {
         if (valid) {
-          uint16_t* op = args.expert_out + static_cast<size_t>(row) * H + ti.nt * TILE_N + h * 128;
+          float* op = args.expert_out + static_cast<size_t>(row) * H + ti.nt * TILE_N + h * 128;
 #pragma unroll
-          for (int v = 0; v < 16; ++v) {
-            uint32_t o[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(ACC(v * 8 + u * 2), ACC(v * 8 + u * 2 + 1));
-              o[u] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            reinterpret_cast<uint4*>(op)[v] = make_uint4(o[0], o[1], o[2], o[3]);
-          }
+          for (int v = 0; v < 32; ++v)
+            reinterpret_cast<float4*>(op)[v] = make_float4(ACC(4 * v), ACC(4 * v + 1), ACC(4 * v + 2), ACC(4 * v + 3));
         }
       }
     }

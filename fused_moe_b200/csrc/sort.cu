@@ -135,9 +135,10 @@ k_gather(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_sc
 }
 
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
+// Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).
 __global__ void __launch_bounds__(128)
-k_reduce(const uint16_t* __restrict__ expert_out, const int* __restrict__ scatter_map,
-         const float* __restrict__ topk_w, int T, uint16_t* __restrict__ out) {
+k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
+         int T, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
   const int t = blockIdx.x;
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
@@ -155,21 +156,27 @@ k_reduce(const uint16_t* __restrict__ expert_out, const int* __restrict__ scatte
       int pos = s_pos[k];
       if (pos < 0) continue;
       float w = s_w[k];
-      uint4 q = __ldg(reinterpret_cast<const uint4*>(expert_out + static_cast<size_t>(pos) * H) + v);
-      uint32_t u[4] = {q.x, q.y, q.z, q.w};
+      const float4* src = reinterpret_cast<const float4*>(expert_out + static_cast<size_t>(pos) * H) + 2 * v;
+      float4 a = __ldg(src), b = __ldg(src + 1);
+      acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]);
+      acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
+      acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]);
+      acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
+    }
+    if (out) {
+      uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        acc[2 * j] = fmaf(w, __uint_as_float(u[j] << 16), acc[2 * j]);
-        acc[2 * j + 1] = fmaf(w, __uint_as_float(u[j] & 0xffff0000u), acc[2 * j + 1]);
+        __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&b);
       }
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-      o[j] = *reinterpret_cast<uint32_t*>(&b);
+    if (out_f32) {
+      float4* dst = reinterpret_cast<float4*>(out_f32 + static_cast<size_t>(t) * H) + 2 * v;
+      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
-    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -208,7 +215,7 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
 int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
-  k_reduce<<<p->T, 128, 0, st>>>(ws->expert_out, ws->scatter_map, w, p->T, p->output);
+  k_reduce<<<p->T, 128, 0, st>>>(ws->expert_out, ws->scatter_map, w, p->T, p->output, p->output_f32);
   B200MOE_CUDA_TRY(cudaGetLastError());
   return B200MOE_OK;
 }

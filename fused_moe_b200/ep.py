@@ -9,7 +9,7 @@ The reference is single-GPU: its only hook for sharding is ``local_expert_offset
      every rank that owns at least one of its experts — group-limited routing bounds that by 4 ranks at G = 8;
   3. the receiver runs the layer on what arrived (``kernel_from_topk``: sort, gather, GEMM1+SwiGLU, GEMM2, reduce over
      ITS experts only), giving one partial row per received token, already weighted and summed over its experts;
-  4. combine: partial rows return to the token's home rank, which adds them in fp32 and rounds to bf16.
+  4. combine: fp32 partial rows return to the token's home rank, which adds them and rounds once to bf16.
 
 Collectives are two ``all_to_all_single`` per direction (split sizes, then payload) over NCCL (NVLink/NVSwitch); payloads
 land in local HBM before any kernel reads them.  Routing and the expert path are injected callables, so the same
@@ -97,8 +97,9 @@ class ExpertParallelMoE:
     """One rank's shard of the layer.
 
     route_fn(logits [T,256], bias [256], scale) -> (topk_idx int32 [T,8], topk_w fp32 [T,8])
-    expert_fn(topk_idx [n,8], topk_w [n,8], hidden e4m3 [n,7168], scales [56,n]) -> partial rows bf16 [n,7168]
-              (sum over THIS rank's experts of weight * expert output; zeros where none is local)
+    expert_fn(topk_idx [n,8], topk_w [n,8], hidden e4m3 [n,7168], scales [56,n]) -> partial rows fp32 [n,7168]
+              (sum over THIS rank's experts of weight * expert output; zeros where none is local).  Partials stay in
+              fp32 until the home rank has added them: rounding each shard's share to bf16 first costs accuracy.
     """
 
     def __init__(self, route_fn: Callable, expert_fn: Callable, rank: int, world: int, group=None):
@@ -128,7 +129,7 @@ class ExpertParallelMoE:
         partial = self.expert_fn(idx, w, hs, scales)
         back = _a2a(partial, plan.recv_splits, plan.send_splits, self.world, self.group)
         acc = torch.zeros((T, H), dtype=torch.float32, device=hidden_states.device)
-        acc.index_add_(0, plan.send_token, back.float())
+        acc.index_add_(0, plan.send_token, back.float())  # back is fp32 already on the CUDA path
         if output is None:
             return acc.to(torch.bfloat16)
         output.copy_(acc)
@@ -147,6 +148,7 @@ def make_cuda_shard(weights: dict, rank: int, world: int, group=None) -> ExpertP
 
     def expert_fn(idx, w, hs, scales):
         return K.kernel_from_topk(idx, w, hs, scales, weights["gemm1_weights"], weights["gemm1_weights_scale"],
-                                  weights["gemm2_weights"], weights["gemm2_weights_scale"], offset)
+                                  weights["gemm2_weights"], weights["gemm2_weights_scale"], offset,
+                                  out_dtype=torch.float32)
 
     return ExpertParallelMoE(route_fn, expert_fn, rank, world, group)

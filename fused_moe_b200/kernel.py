@@ -126,7 +126,10 @@ def _problem(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w
     p.gemm1_weights_scale = w13s.data_ptr()
     p.gemm2_weights = w2.data_ptr()
     p.gemm2_weights_scale = w2s.data_ptr()
-    p.output = out.data_ptr()
+    if out.dtype == torch.float32:
+        p.output, p.output_f32 = None, out.data_ptr()
+    else:
+        p.output, p.output_f32 = out.data_ptr(), None
     p.topk_idx_in = topk_idx.data_ptr() if topk_idx is not None else None
     p.topk_w_in = topk_w.data_ptr() if topk_w is not None else None
     return p
@@ -145,7 +148,8 @@ def _check_weights(hidden_states, gemm1_weights, gemm1_weights_scale, gemm2_weig
     return E_local, w13, w13s, w2, w2s
 
 
-def _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, topk_idx, topk_w):
+def _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, topk_idx, topk_w,
+         out_dtype=torch.bfloat16):
     _require_cuda(routing_logits=logits, routing_bias=bias, hidden_states=hs, hidden_states_scale=hs_scale,
                   gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2, gemm2_weights_scale=w2s,
                   topk_idx=topk_idx, topk_weights=topk_w)
@@ -153,10 +157,10 @@ def _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w
     if offset < 0 or offset + E_local > E_GLOBAL:
         raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")
     if output is None:
-        output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        output = torch.empty((T, H), dtype=out_dtype, device=device)
     else:
-        if output.dtype != torch.bfloat16 or tuple(output.shape) != (T, H) or not output.is_contiguous():
-            raise ValueError("output must be a contiguous bfloat16 tensor of shape [T, 7168]")
+        if output.dtype != out_dtype or tuple(output.shape) != (T, H) or not output.is_contiguous():
+            raise ValueError(f"output must be a contiguous {out_dtype} tensor of shape [T, 7168]")
         if output.device != device:
             raise RuntimeError("output must live on the device of hidden_states")
     if T == 0:
@@ -212,10 +216,15 @@ def kernel(
 
 @torch.no_grad()
 def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
-                     gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None):
+                     gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None,
+                     out_dtype=torch.bfloat16):
     """Same layer for tokens whose routing already ran (expert-parallel receiver): ``topk_idx`` [T,8] int32 global
     expert ids and ``topk_weights`` [T,8] f32 final weights replace logits, bias and scaling factor.  Only pairs whose
-    expert lies in [offset, offset+E) contribute.  The reference has no such entry (single GPU only)."""
+    expert lies in [offset, offset+E) contribute.  ``out_dtype=torch.float32`` returns the sums before the bfloat16
+    rounding, which is how a shard's partial results travel back to the tokens' home ranks.  The reference has no such
+    entry (single GPU only)."""
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("out_dtype must be torch.bfloat16 or torch.float32")
     if not torch.is_tensor(topk_idx) or topk_idx.dim() != 2:
         raise ValueError("topk_idx must be [T, 8]")
     T = int(topk_idx.shape[0])
@@ -226,7 +235,7 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
     hs = _require(hidden_states, "hidden_states", _FP8, (T, H))
     hs_scale = _require(hidden_states_scale, "hidden_states_scale", torch.float32, (H_BLOCKS, T))
     offset = _host_scalar(local_expert_offset, int)
-    return _run(T, E_local, offset, 1.0, None, None, hs, hs_scale, w13, w13s, w2, w2s, output, idx, w)
+    return _run(T, E_local, offset, 1.0, None, None, hs, hs_scale, w13, w13s, w2, w2s, output, idx, w, out_dtype)
 
 
 @torch.no_grad()

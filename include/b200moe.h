@@ -57,6 +57,8 @@ enum {
  *   gemm2_weights         [E_local, 7168, 2048] e4m3fn
  *   gemm2_weights_scale   [E_local, 56, 16]   float32
  *   output                [T, 7168]           bfloat16; every row is written (zeros for tokens with no local expert)
+ *   output_f32            [T, 7168]           float32, optional: the same sums before the bfloat16 rounding (partial
+ *                                             results of an expert-parallel shard travel in this form)
  *
  * If routing_logits is NULL the routing stage is skipped and (topk_idx_in, topk_w_in) — [T,8] int32 global expert
  * ids and [T,8] float32 final weights — are used instead.  This is the path the expert-parallel receiver takes for
@@ -78,6 +80,7 @@ typedef struct b200moe_problem {
   uint16_t* output;
   const int32_t* topk_idx_in;
   const float* topk_w_in;
+  float* output_f32; /* optional [T,7168] float32: if non-NULL the un-rounded sums go here and `output` may be NULL */
 } b200moe_problem;
 
 /* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
@@ -107,7 +110,7 @@ typedef struct b200moe_workspace {
   float* a_scale_sorted;     /* [56, R_max]   their scales, k-block major */
   uint8_t* inter_q;          /* [2, R_max, 2048] e4m3: SwiGLU output as value term + residual term, shared scale */
   float* inter_scale;        /* [16, R_max]   per row per 128 columns */
-  uint16_t* expert_out;      /* [R_max, 7168] bf16 GEMM2 result per sorted row (unweighted) */
+  float* expert_out;         /* [R_max, 7168] float32 GEMM2 result per sorted row (unweighted) */
 } b200moe_workspace;
 
 /* Library / build identification.  No reference counterpart. */
@@ -154,11 +157,11 @@ int b200moe_gather(const b200moe_problem* p, const b200moe_workspace* ws, void* 
  * Replaces _fused_moe_gemm1_swiglu_kernel (solution/python/pure_triton_impl.py:886-1046) and the CuTe GEMM1 chain
  * (solution/python/cute_gemm1_mma.py:247-289, solution/python/triton_impl.py:113-150). */
 int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
-/* Grouped FP8 GEMM2 over the two-term intermediate, bf16 rows out.
+/* Grouped FP8 GEMM2 over the two-term intermediate, float32 rows out.
  * Replaces _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196) and the CuTe GEMM2
  * (solution/python/cute_gemm2_mma.py:250-304). */
 int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
-/* out[t] = sum_k topk_w[t,k] * expert_out[scatter_map[t,k]], fp32 accumulate, bf16 store, no atomics.
+/* out[t] = sum_k topk_w[t,k] * expert_out[scatter_map[t,k]], fp32 accumulate, bf16 (and/or fp32) store, no atomics.
  * Replaces _token_reduce_kernel (solution/python/pure_triton_impl.py:1758-1821) and
  * _token_reduce_weighted_kernel (solution/python/triton_impl.py:163-207). */
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
