@@ -11,7 +11,8 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "libb200moe.so"
 
-OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED = 0, -1, -2, -3, -4, -5
+OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3, -4, -5, -6
+SORT_STATIC_MAX_ENTRIES = 32768
 
 
 class Problem(C.Structure):
@@ -81,6 +82,7 @@ SYMBOLS = {
     "b200moe_gemm1": (C.c_int, _PW),
     "b200moe_gemm2": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),
+    "b200moe_sort_static": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32) + (C.c_void_p,) * 7),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),
 }
 

@@ -136,6 +136,7 @@ const char* b200moe_strerror(int code) {
     case B200MOE_ECUDA: return "CUDA call failed";
     case B200MOE_EDEVICE: return "device status word reports a failed kernel";
     case B200MOE_EUNSUPPORTED: return "current device is not an sm_100 GPU";
+    case B200MOE_ETOOLARGE: return "problem exceeds the fixed scratch capacity of this entry point";
     default: return "unknown error";
   }
 }

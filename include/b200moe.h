@@ -43,7 +43,8 @@ enum {
   B200MOE_EWORKSPACE = -2,/* workspace too small or misaligned */
   B200MOE_ECUDA = -3,     /* a CUDA runtime / driver call failed; see b200moe_last_cuda_error() */
   B200MOE_EDEVICE = -4,   /* a kernel recorded a failure in the device status word (bounded wait ran out) */
-  B200MOE_EUNSUPPORTED = -5 /* the current device is not sm_100 */
+  B200MOE_EUNSUPPORTED = -5,/* the current device is not sm_100 */
+  B200MOE_ETOOLARGE = -6    /* the problem exceeds the fixed capacity of an entry point that allocates nothing */
 };
 
 /* Inputs and output of one layer call.  Tensor layouts are exactly those of the reference operator
@@ -165,6 +166,24 @@ int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
  * Replaces _token_reduce_kernel (solution/python/pure_triton_impl.py:1758-1821) and
  * _token_reduce_weighted_kernel (solution/python/triton_impl.py:163-207). */
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+
+/* Token sort for callers that cannot allocate device memory (a process that gave all of HBM to its own pool, a plugin
+ * with a memory budget fixed at start-up, a region where allocation is forbidden).  Same results as b200moe_topk_bits
+ * + b200moe_sort — counts[E_local], block_offsets[E_local+1], total_blocks[1], sorted_token_ids / sorted_weights
+ * [(8*T/128 + E_local)*128], scatter_map[T*8] (16-byte aligned), all caller-owned device buffers — computed from
+ * topk_idx / topk_w [T,8].  The two scratch tables live in a fixed array inside the library, so the call uses no
+ * allocator of any kind.  Limits and rules:
+ *   - ceil(T/32) * E_local <= B200MOE_SORT_STATIC_MAX_ENTRIES, else B200MOE_ETOOLARGE (e.g. T <= 32768 at 32 local
+ *     experts, T <= 4096 at 256);
+ *   - every GPU that loads the library holds the array (256 KB) until the process exits;
+ *   - all calls on one GPU share the array: calls whose kernels overlap on the device race; serialise them;
+ *   - the first call on each GPU looks up the array's device address (with that GPU current); make that first call
+ *     before any stream capture begins.
+ * This entry point has no counterpart in the reference. */
+#define B200MOE_SORT_STATIC_MAX_ENTRIES 32768
+int b200moe_sort_static(const int32_t* topk_idx, const float* topk_w, int32_t T, int32_t E_local,
+                        int32_t local_expert_offset, int32_t* counts, int32_t* block_offsets, int32_t* total_blocks,
+                        int32_t* sorted_token_ids, float* sorted_weights, int32_t* scatter_map, void* stream);
 
 /* Synchronises `stream`, copies the device status word to *status (host) and clears it.
  * Returns B200MOE_EDEVICE if it was non-zero.  No reference counterpart (the reference has no device-side waits). */
