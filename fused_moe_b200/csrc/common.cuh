@@ -184,6 +184,28 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
+// Programmatic dependent launch: every kernel of the layer lets its successor be scheduled early
+// (pdl_launch_dependents at entry) and blocks in pdl_wait until its predecessor has completed and flushed before it
+// touches global memory.  Only launch latency and per-CTA set-up overlap; data dependences stay kernel-to-kernel.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Launch-side error helper used by the .cu files.
 #define B200MOE_CUDA_TRY(expr)                                   \
   do {                                                           \

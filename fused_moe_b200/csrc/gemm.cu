@@ -131,8 +131,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int E = args.E_local;
   constexpr int NT = C::N_TILES;
 
-  for (int i = threadIdx.x; i <= E; i += GEMM_THREADS) aux->off[i] = __ldg(args.block_offsets + i);
-  for (int i = threadIdx.x; i < E; i += GEMM_THREADS) aux->cnt[i] = __ldg(args.counts + i);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) aux->abort_flag = 0;
 
   if (warp == PRODUCER_WARP && lane == 0) {
@@ -153,6 +152,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tmem_alloc(smem_u32(&aux->tmem_base), 512);
     tmem_relinquish();
   }
+  // everything above is CTA-local set-up and may overlap the tail of the previous kernel; the layout it wrote is
+  // read only from here on
+  pdl_wait();
+  for (int i = threadIdx.x; i <= E; i += GEMM_THREADS) aux->off[i] = __ldg(args.block_offsets + i);
+  for (int i = threadIdx.x; i < E; i += GEMM_THREADS) aux->cnt[i] = __ldg(args.counts + i);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -442,8 +446,7 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
     a.row_scale = ws->inter_scale;
     a.w_scale = p->gemm2_weights_scale;
   }
-  k_grouped_gemm<MODE><<<num_sms, GEMM_THREADS, smem, st>>>(tmA, tmB, a);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_grouped_gemm<MODE>, dim3(num_sms), dim3(GEMM_THREADS), smem, st, tmA, tmB, a));
   return B200MOE_OK;
 }
 

@@ -58,7 +58,9 @@ k_route(const float* __restrict__ logits, const uint16_t* __restrict__ bias, int
   const int chunk = blockIdx.x;
   const int t = chunk * 32 + warp;
 
+  pdl_launch_dependents();
   if (threadIdx.x < E_GLOBAL) s_bits[threadIdx.x] = 0;
+  pdl_wait();
   __syncthreads();
 
   if (t < T) {
@@ -142,6 +144,8 @@ k_topk_bits(const int* __restrict__ topk_idx, int T, int local_offset, int E_loc
             uint32_t* __restrict__ chunk_bits) {
   const int lane = threadIdx.x & 31;
   const int chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
   if (chunk >= n_chunks) return;
   const int t = chunk * 32 + lane;
   uint32_t mask[E_GLOBAL / 32];
@@ -174,10 +178,9 @@ k_topk_bits(const int* __restrict__ topk_idx, int T, int local_offset, int E_loc
 
 int launch_route(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
-  k_route<<<ws->n_chunks, 1024, 0, st>>>(p->routing_logits, p->routing_bias, p->T, p->routed_scaling_factor,
-                                         p->local_expert_offset, p->E_local, ws->topk_idx, ws->topk_w,
-                                         ws->chunk_bits);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_route, dim3(ws->n_chunks), dim3(1024), 0, st, p->routing_logits, p->routing_bias, p->T,
+                              p->routed_scaling_factor, p->local_expert_offset, p->E_local, ws->topk_idx, ws->topk_w,
+                              ws->chunk_bits));
   return B200MOE_OK;
 }
 
@@ -185,9 +188,8 @@ int launch_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, cuda
   if (p->T == 0) return B200MOE_OK;
   int grid = (ws->n_chunks + 3) / 4;
   const int* idx = p->routing_logits ? ws->topk_idx : p->topk_idx_in;
-  k_topk_bits<<<grid, 128, 0, st>>>(idx, p->T, p->local_expert_offset, p->E_local, ws->n_chunks,
-                                    ws->chunk_bits);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_topk_bits, dim3(grid), dim3(128), 0, st, idx, p->T, p->local_expert_offset, p->E_local,
+                              ws->n_chunks, ws->chunk_bits));
   return B200MOE_OK;
 }
 

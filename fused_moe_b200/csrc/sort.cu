@@ -19,6 +19,8 @@ k_rank_scan(const uint32_t* __restrict__ chunk_bits, int n_chunks, int E_local, 
             int* __restrict__ counts) {
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
   if (e >= E_local) return;
   int running = 0;
   for (int base = 0; base < n_chunks; base += 32) {
@@ -46,6 +48,8 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, co
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
 
+  pdl_launch_dependents();
+  pdl_wait();
   if (warp == 0) {
     // lane handles experts [8*lane, 8*lane+8)
     int blocks[8];
@@ -121,6 +125,8 @@ k_gather(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_sc
          uint8_t* __restrict__ a_sorted, float* __restrict__ a_scale_sorted) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   const int rows = __ldg(total_blocks) * BLOCK_M;
   for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
     int tok = __ldg(sorted_token_ids + r);
@@ -142,6 +148,8 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   const int t = blockIdx.x;
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x < TOP_K) {
     s_pos[threadIdx.x] = __ldg(scatter_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
     s_w[threadIdx.x] = __ldg(topk_w + static_cast<size_t>(t) * TOP_K + threadIdx.x);
@@ -190,13 +198,12 @@ int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStrea
     return B200MOE_OK;
   }
   int scan_grid = (p->E_local + 31) / 32;
-  k_rank_scan<<<scan_grid, 1024, 0, st>>>(ws->chunk_bits, ws->n_chunks, p->E_local, ws->chunk_base, ws->counts);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_rank_scan, dim3(scan_grid), dim3(1024), 0, st, ws->chunk_bits, ws->n_chunks, p->E_local,
+                              ws->chunk_base, ws->counts));
   int grid = (ws->n_chunks + 3) / 4;
-  k_scatter<<<grid, 128, 0, st>>>(idx, w, ws->chunk_bits, ws->chunk_base, ws->counts, p->T, p->local_expert_offset,
-                                  p->E_local, ws->n_chunks, ws->block_offsets, ws->total_blocks,
-                                  ws->sorted_token_ids, ws->sorted_weights, ws->scatter_map);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_scatter, dim3(grid), dim3(128), 0, st, idx, w, ws->chunk_bits, ws->chunk_base,
+                              ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks, ws->block_offsets,
+                              ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights, ws->scatter_map));
   return B200MOE_OK;
 }
 
@@ -206,17 +213,16 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
   int grid = static_cast<int>((max_rows + 7) / 8);
   if (grid > num_sms * 8) grid = num_sms * 8;
   if (grid < 1) grid = 1;
-  k_gather<<<grid, 256, 0, st>>>(p->hidden_states, p->hidden_states_scale, p->T, ws->sorted_token_ids,
-                                 ws->total_blocks, ws->R_max, ws->a_sorted, ws->a_scale_sorted);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_gather, dim3(grid), dim3(256), 0, st, p->hidden_states, p->hidden_states_scale, p->T,
+                              ws->sorted_token_ids, ws->total_blocks, ws->R_max, ws->a_sorted, ws->a_scale_sorted));
   return B200MOE_OK;
 }
 
 int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
-  k_reduce<<<p->T, 128, 0, st>>>(ws->expert_out, ws->scatter_map, w, p->T, p->output, p->output_f32);
-  B200MOE_CUDA_TRY(cudaGetLastError());
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w, p->T,
+                              p->output, p->output_f32));
   return B200MOE_OK;
 }
 
