@@ -85,6 +85,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-level form: every lane polls and the warp agrees on the outcome (all lanes polling measured faster on B200
+// than one elected lane with the rest parked at a warp barrier every time: 967 vs 1204 cycles per GEMM chunk; roles
+// that only ever need one thread run their whole loop as lane 0 instead).
+__device__ __forceinline__ bool mbar_wait_all(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                              int role, int detail) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, role, detail));
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor, no multicast anywhere)
 // ---------------------------------------------------------------------------------------------------------

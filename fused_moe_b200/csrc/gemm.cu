@@ -169,18 +169,19 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp >= NUM_PROMO_WARPS) {
   setmaxnreg_dec_aux();
   if (warp == PRODUCER_WARP) {
-    // ------------------------------------------------------------------ TMA producer (lane 0 issues, warp stays converged)
-    int stage = 0;
-    uint32_t phase = 0;
-    long long issued = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
-      for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, abort_flag, args.status, 1, kb));
-        if (!ok) break;
-        if (lane == 0) {
+    // ------------------------------------------------------------------ TMA producer (one thread)
+    // The two single-thread roles run as lane 0 alone: one poller per barrier and no per-chunk warp votes.  (Measured:
+    // all 32 lanes voting on every wait cost the MMA issuer ~300 idle cycles per chunk.)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
+        for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
+          ok = mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, abort_flag, args.status, 1, kb);
+          if (!ok) break;
           const uint32_t full = smem_u32(&aux->full[stage]);
           const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
           mbar_arrive_expect_tx(full, C::STAGE_BYTES);
@@ -193,37 +194,36 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_load_2d(sbase + A_TILE_BYTES, &tmA, full, kb * 128, args.R_max + ti.mblk * BLOCK_M);
             tma_load_2d(sbase + 2 * A_TILE_BYTES, &tmB, full, kb * 128, ti.e * H + ti.nt * TILE_N);
           }
+          ++issued;
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        ++issued;
-        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
-    }
-    if (!ok && lane == 0) {
-      // Drain: every load already issued completes on its own; wait (bounded) so none lands after the CTA exits.
-      for (int s = 0; s < C::STAGES; ++s) {
-        long long n_s = issued / C::STAGES + ((issued % C::STAGES) > s ? 1 : 0);  // loads issued to stage s
-        if (n_s == 0) continue;
-        uint32_t par = static_cast<uint32_t>((n_s - 1) & 1);
-        for (int spin = 0; spin < (1 << 20); ++spin)
-          if (mbar_try_wait(smem_u32(&aux->full[s]), par)) break;
+      if (!ok) {
+        // Drain: every load already issued completes on its own; wait (bounded) so none lands after the CTA exits.
+        for (int s = 0; s < C::STAGES; ++s) {
+          long long n_s = issued / C::STAGES + ((issued % C::STAGES) > s ? 1 : 0);  // loads issued to stage s
+          if (n_s == 0) continue;
+          uint32_t par = static_cast<uint32_t>((n_s - 1) & 1);
+          for (int spin = 0; spin < (1 << 20); ++spin)
+            if (mbar_try_wait(smem_u32(&aux->full[s]), par)) break;
+        }
       }
     }
     __syncwarp();
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer (lane 0 issues, warp stays converged)
-    constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M, TILE_N);
-    int stage = 0, acc = 0;
-    uint32_t phase = 0, acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb) &&
-                            mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb));
-        if (!ok) break;
-        tc_fence_after();
-        if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M, TILE_N);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
+          ok = mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb);
+          if (!ok) break;
+          ok = mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb);
+          if (!ok) break;
+          tc_fence_after();
           const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
           const uint32_t d = tmem_base + static_cast<uint32_t>(acc * TILE_N);
           const uint64_t a0 = umma_desc_sw128(sbase);
@@ -237,13 +237,13 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           tc_commit(smem_u32(&aux->empty[stage]));
           tc_commit(smem_u32(&aux->tfull[acc]));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        __syncwarp();
-        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
       }
     }
+    __syncwarp();
   }
   } else {
     setmaxnreg_inc_promo();
@@ -286,7 +286,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           w0_n = __ldg(ws0_ptr + kb + 1);
           w1_n = __ldg(ws1_ptr + kb + 1);
         }
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tfull[acc]), acc_phase, abort_flag, args.status, 4, kb));
+        ok = mbar_wait_all(smem_u32(&aux->tfull[acc]), acc_phase, abort_flag, args.status, 4, kb);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * TILE_N) + (static_cast<uint32_t>(q * 32) << 16);
@@ -330,8 +330,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // the other column half of each row lives in warp (w ^ 4): exchange through shared memory, bounded wait
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&aux->xbar[tile_iter & 1]));
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->xbar[tile_iter & 1]), (tile_iter >> 1) & 1, abort_flag,
-                                               args.status, 5, tile_iter));
+        ok = mbar_wait_all(smem_u32(&aux->xbar[tile_iter & 1]), (tile_iter >> 1) & 1, abort_flag, args.status, 5,
+                            tile_iter);
         if (!ok) break;
         amax = fmaxf(ex[r_in_tile], ex[BLOCK_M + r_in_tile]);
         const float s = fmaxf(amax, 1e-20f) * (1.0f / 448.0f);
