@@ -177,9 +177,10 @@ class _Null:
         return False
 
 
-def stage_times(K, inp, T, E_local, offset, reps=5, topk=None):
+def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
     """CUDA-event duration (us) of each stage kernel, launched on its own through the stage entry points.  With
-    `topk` = (ids, weights) the routing stage is replaced by the chunk-bits stage (expert-parallel receiver)."""
+    `records` (expert-parallel receive buffer) the routing stage is replaced by the chunk-bits stage and the kernels
+    read the records in place."""
     from fused_moe_b200 import _lib
     from fused_moe_b200.kernel import _problem, _workspace
     lib = _lib.load()
@@ -187,12 +188,19 @@ def stage_times(K, inp, T, E_local, offset, reps=5, topk=None):
     stream = torch.cuda.current_stream().cuda_stream
     ws = _workspace(dev, T, E_local, stream)
     out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]),
-                 None if topk else inp["routing_logits"], None if topk else inp["routing_bias"],
-                 inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"],
-                 inp["gemm2_weights"], inp["gemm2_weights_scale"], out, *(topk or (None, None)))
+    if records is None:
+        p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]), inp["routing_logits"],
+                     inp["routing_bias"], inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"],
+                     inp["gemm1_weights_scale"], inp["gemm2_weights"], inp["gemm2_weights_scale"], out)
+    else:
+        p = _lib.Problem()
+        _lib.check(lib.b200moe_ep_record_layout(records.data_ptr(), T, C.byref(p)), "record_layout")
+        p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
+        p.gemm1_weights, p.gemm1_weights_scale = inp["gemm1_weights"].data_ptr(), inp["gemm1_weights_scale"].data_ptr()
+        p.gemm2_weights, p.gemm2_weights_scale = inp["gemm2_weights"].data_ptr(), inp["gemm2_weights_scale"].data_ptr()
+        p.output = out.data_ptr()
     res = {}
-    for name in ("topk_bits" if topk else "route", "sort", "gather", "gemm1", "gemm2", "reduce"):
+    for name in ("topk_bits" if records is not None else "route", "sort", "gather", "gemm1", "gemm2", "reduce"):
         fn = getattr(lib, "b200moe_" + name)
         _lib.check(fn(C.byref(p), C.byref(ws.struct), stream), name)  # warm
         torch.cuda.synchronize()
@@ -308,9 +316,8 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     if world == 1:
         st, pairs, active, blocks = stage_times(K, inp, T_loc, E_local, offset)
     else:
-        idx, w, hs, scales = shard.last_recv
-        recv = dict(inp, hidden_states=hs, hidden_states_scale=scales)
-        st, pairs, active, blocks = stage_times(K, recv, idx.shape[0], E_local, offset, topk=(idx, w))
+        recs = shard.last_records
+        st, pairs, active, blocks = stage_times(K, inp, recs.shape[0], E_local, offset, records=recs)
     rec.update(stage_us=st, pairs=pairs, active_experts=active, row_blocks=blocks)
     return rec, inp
 

@@ -13,6 +13,7 @@ LIB_PATH = PKG_DIR / "libb200moe.so"
 
 OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3, -4, -5, -6
 SORT_STATIC_MAX_ENTRIES = 32768
+EP_RECORD_BYTES = 7456
 
 
 class Problem(C.Structure):
@@ -35,6 +36,10 @@ class Problem(C.Structure):
         ("topk_idx_in", C.c_void_p),
         ("topk_w_in", C.c_void_p),
         ("output_f32", C.c_void_p),
+        ("hidden_row_stride", C.c_int64),
+        ("scale_token_stride", C.c_int64),
+        ("scale_block_stride", C.c_int64),
+        ("topk_row_stride", C.c_int64),
     ]
 
 
@@ -83,6 +88,10 @@ SYMBOLS = {
     "b200moe_gemm2": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),
     "b200moe_sort_static": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32) + (C.c_void_p,) * 7),
+    "b200moe_ep_scratch_bytes": (C.c_int, (C.c_int32, C.c_int32, C.POINTER(C.c_size_t))),
+    "b200moe_ep_dispatch": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.c_int32, C.c_void_p, C.c_size_t) + (C.c_void_p,) * 4),
+    "b200moe_ep_record_layout": (C.c_int, (C.c_void_p, C.c_int32, C.POINTER(Problem))),
+    "b200moe_ep_combine": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),
 }
 

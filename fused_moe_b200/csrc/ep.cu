@@ -1,0 +1,231 @@
+// Expert-parallel dispatch and combine (the reference is single-GPU and has neither).
+//
+// Dispatch: a token goes once to every rank that owns one of its eight experts.  The (token, destination) pairs are
+// ranked with the same bit-matrix trick as the expert sort (sort.cu): chunk_bits[c][d] has bit j set when token 32c+j
+// needs rank d, the per-destination prefix over chunks gives each pair its position, and the order — by destination,
+// then by token id — is deterministic.  One warp then writes each 7456-byte record (activations, 56 scales, the eight
+// expert ids and weights) into the send buffer, laid out so that a plain all-to-all with `send_counts` rows per
+// destination delivers contiguous segments.  The receiver's kernels read the records in place through the strides of
+// b200moe_problem.
+//
+// Combine: the float32 rows that come back in the same order are summed per token in slot order and rounded once.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int EP_RECORD = B200MOE_EP_RECORD_BYTES;  // 7168 + 224 + 32 + 32
+
+int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* counts, cudaStream_t st);
+int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st);
+
+// chunk_bits over destination ranks: one warp per 32-token chunk, lane = token.
+__global__ void __launch_bounds__(128)
+k_dest_bits(const int* __restrict__ topk_idx, int T, int experts_per_rank, int world, int n_chunks,
+            uint32_t* __restrict__ chunk_bits) {
+  const int lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (chunk >= n_chunks) return;
+  const int t = chunk * 32 + lane;
+  uint32_t mask[E_GLOBAL / 32];
+#pragma unroll
+  for (int i = 0; i < E_GLOBAL / 32; ++i) mask[i] = 0;
+  if (t < T) {
+#pragma unroll
+    for (int k = 0; k < TOP_K; ++k) {
+      const int d = __ldg(topk_idx + static_cast<size_t>(t) * TOP_K + k) / experts_per_rank;
+#pragma unroll
+      for (int i = 0; i < E_GLOBAL / 32; ++i)
+        if (i == (d >> 5)) mask[i] |= 1u << (d & 31);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E_GLOBAL / 32; ++i) {
+    if (i * 32 >= world) break;
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      uint32_t w = __ballot_sync(0xffffffffu, (mask[i] >> j) & 1u);
+      if (lane == j) mine = w;
+    }
+    const int d = i * 32 + lane;
+    if (d < world) chunk_bits[static_cast<size_t>(chunk) * world + d] = mine;
+  }
+}
+
+// Record index of every (token, destination) pair: segment start of the destination + rank of the token inside it.
+// slot_map[t,k] gets the index for the FIRST of the token's experts that lives on that destination, -1 for the others.
+__global__ void __launch_bounds__(128)
+k_dispatch_slots(const int* __restrict__ topk_idx, const uint32_t* __restrict__ chunk_bits,
+                 const int* __restrict__ chunk_base, const int* __restrict__ counts, int T, int experts_per_rank,
+                 int world, int n_chunks, int* __restrict__ send_counts, int* __restrict__ slot_token,
+                 int* __restrict__ slot_map) {
+  __shared__ int s_seg[E_GLOBAL + 1];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (warp == 0) {
+    int c[8], local = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane * 8 + i;
+      c[i] = (d < world) ? __ldg(counts + d) : 0;
+      local += c[i];
+    }
+    int incl = local;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      int o = __shfl_up_sync(0xffffffffu, incl, s);
+      if (lane >= s) incl += o;
+    }
+    int run = incl - local;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane * 8 + i;
+      if (d < world) s_seg[d] = run;
+      run += c[i];
+    }
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int d = threadIdx.x; d < world; d += blockDim.x) send_counts[d] = __ldg(counts + d);
+
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (chunk >= n_chunks) return;
+  const int t = chunk * 32 + lane;
+  if (t >= T) return;
+  const uint32_t below = (1u << lane) - 1u;
+  int dest[TOP_K], slot[TOP_K];
+#pragma unroll
+  for (int k = 0; k < TOP_K; ++k) {
+    dest[k] = __ldg(topk_idx + static_cast<size_t>(t) * TOP_K + k) / experts_per_rank;
+    bool first = true;
+#pragma unroll
+    for (int j = 0; j < k; ++j) first = first && (dest[j] != dest[k]);
+    slot[k] = -1;
+    if (first) {
+      const int d = dest[k];
+      const uint32_t bits = __ldg(chunk_bits + static_cast<size_t>(chunk) * world + d);
+      const int s = s_seg[d] + __ldg(chunk_base + static_cast<size_t>(chunk) * world + d) + __popc(bits & below);
+      slot[k] = s;
+      slot_token[s] = t;
+    }
+  }
+  int4* out = reinterpret_cast<int4*>(slot_map + static_cast<size_t>(t) * TOP_K);
+  out[0] = make_int4(slot[0], slot[1], slot[2], slot[3]);
+  out[1] = make_int4(slot[4], slot[5], slot[6], slot[7]);
+}
+
+// One warp per record.
+__global__ void __launch_bounds__(256)
+k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale,
+               const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int T, const int* __restrict__ counts,
+               int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  int total = 0;
+  for (int d = 0; d < world; ++d) total += __ldg(counts + d);
+  for (int s = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); s < total; s += gridDim.x * warps_per_cta) {
+    const int tok = __ldg(slot_token + s);
+    uint8_t* rec = send_rows + static_cast<size_t>(s) * EP_RECORD;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
+    uint4* dst = reinterpret_cast<uint4*>(rec);
+#pragma unroll
+    for (int i = 0; i < H / 16 / 32; ++i) dst[i * 32 + lane] = __ldg(src + i * 32 + lane);
+    float* sc = reinterpret_cast<float*>(rec + H);
+    for (int kb = lane; kb < H_BLOCKS; kb += 32) sc[kb] = __ldg(hidden_scale + static_cast<size_t>(kb) * T + tok);
+    if (lane < TOP_K) {
+      reinterpret_cast<int*>(rec + H + 4 * H_BLOCKS)[lane] = __ldg(topk_idx + static_cast<size_t>(tok) * TOP_K + lane);
+      reinterpret_cast<float*>(rec + H + 4 * H_BLOCKS + 4 * TOP_K)[lane] =
+          __ldg(topk_w + static_cast<size_t>(tok) * TOP_K + lane);
+    }
+  }
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_ep_scratch_bytes(int32_t T, int32_t world, size_t* bytes) {
+  if (!bytes || T < 0 || world < 1 || world > E_GLOBAL || E_GLOBAL % world) return B200MOE_EINVAL;
+  const size_t n_chunks = (static_cast<size_t>(T) + 31) / 32;
+  const size_t pairs = static_cast<size_t>(T) * (world < TOP_K ? world : TOP_K);
+  // chunk_bits, chunk_base [n_chunks, world]; counts [world]; slot_token [pairs]; each rounded up to 256 bytes
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  *bytes = 2 * up(4 * n_chunks * world) + up(4 * static_cast<size_t>(world)) + up(4 * pairs);
+  return B200MOE_OK;
+}
+
+int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                        const float* hidden_states_scale, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
+                        uint8_t* send_rows, int32_t* send_counts, int32_t* slot_map, void* stream) {
+  size_t need = 0;
+  int rc = b200moe_ep_scratch_bytes(T, world, &need);
+  if (rc) return rc;
+  if (!send_counts) return B200MOE_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    B200MOE_CUDA_TRY(cudaMemsetAsync(send_counts, 0, sizeof(int32_t) * world, st));
+    return B200MOE_OK;
+  }
+  if (!topk_idx || !topk_w || !hidden_states || !hidden_states_scale || !scratch || !send_rows || !slot_map)
+    return B200MOE_EINVAL;
+  if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u)) return B200MOE_EWORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(send_rows) & 15u) || (reinterpret_cast<uintptr_t>(hidden_states) & 15u) ||
+      (reinterpret_cast<uintptr_t>(slot_map) & 15u))
+    return B200MOE_EINVAL;
+  const int n_chunks = (T + 31) / 32;
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  uint32_t* bits = reinterpret_cast<uint32_t*>(base);
+  int* cbase = reinterpret_cast<int*>(base + up(4 * static_cast<size_t>(n_chunks) * world));
+  int* counts = reinterpret_cast<int*>(base + 2 * up(4 * static_cast<size_t>(n_chunks) * world));
+  int* slot_token = reinterpret_cast<int*>(base + 2 * up(4 * static_cast<size_t>(n_chunks) * world) +
+                                           up(4 * static_cast<size_t>(world)));
+  const int epr = E_GLOBAL / world;
+  const int grid = (n_chunks + 3) / 4;
+  B200MOE_CUDA_TRY(launch_pdl(k_dest_bits, dim3(grid), dim3(128), 0, st, topk_idx, T, epr, world, n_chunks, bits));
+  if ((rc = launch_rank_scan(bits, n_chunks, world, cbase, counts, st))) return rc;
+  B200MOE_CUDA_TRY(launch_pdl(k_dispatch_slots, dim3(grid), dim3(128), 0, st, topk_idx, bits, cbase, counts, T, epr,
+                              world, n_chunks, send_counts, slot_token, slot_map));
+  long long max_pairs = static_cast<long long>(T) * (world < TOP_K ? world : TOP_K);
+  int pgrid = static_cast<int>((max_pairs + 7) / 8);
+  if (pgrid > 148 * 8) pgrid = 148 * 8;
+  B200MOE_CUDA_TRY(launch_pdl(k_pack_records, dim3(pgrid), dim3(256), 0, st, hidden_states, hidden_states_scale,
+                              topk_idx, topk_w, T, counts, world, slot_token, send_rows));
+  return B200MOE_OK;
+}
+
+int b200moe_ep_record_layout(const uint8_t* records, int32_t n, b200moe_problem* p) {
+  if (!p || n < 0 || (n > 0 && !records)) return B200MOE_EINVAL;
+  p->T = n;
+  p->routing_logits = nullptr;
+  p->routing_bias = nullptr;
+  p->hidden_states = records;
+  p->hidden_row_stride = EP_RECORD;
+  p->hidden_states_scale = reinterpret_cast<const float*>(records + H);
+  p->scale_token_stride = EP_RECORD / 4;
+  p->scale_block_stride = 1;
+  p->topk_idx_in = reinterpret_cast<const int32_t*>(records + H + 4 * H_BLOCKS);
+  p->topk_w_in = reinterpret_cast<const float*>(records + H + 4 * H_BLOCKS + 4 * TOP_K);
+  p->topk_row_stride = EP_RECORD / 4;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output,
+                       void* stream) {
+  if (T < 0) return B200MOE_EINVAL;
+  if (T == 0) return B200MOE_OK;
+  if (!returned_rows || !slot_map || !output) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(returned_rows) & 15u) || (reinterpret_cast<uintptr_t>(output) & 15u))
+    return B200MOE_EINVAL;
+  return launch_reduce_rows(returned_rows, slot_map, T, output, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

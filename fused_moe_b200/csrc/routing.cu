@@ -140,7 +140,7 @@ k_route(const float* __restrict__ logits, const uint16_t* __restrict__ bias, int
 
 // chunk_bits from an existing topk_idx: one warp per 32-token chunk, lane = token.
 __global__ void __launch_bounds__(128)
-k_topk_bits(const int* __restrict__ topk_idx, int T, int local_offset, int E_local, int n_chunks,
+k_topk_bits(const int* __restrict__ topk_idx, long long idx_stride, int T, int local_offset, int E_local, int n_chunks,
             uint32_t* __restrict__ chunk_bits) {
   const int lane = threadIdx.x & 31;
   const int chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -154,7 +154,7 @@ k_topk_bits(const int* __restrict__ topk_idx, int T, int local_offset, int E_loc
   if (t < T) {
 #pragma unroll
     for (int k = 0; k < TOP_K; ++k) {
-      int le = __ldg(topk_idx + static_cast<size_t>(t) * TOP_K + k) - local_offset;
+      int le = __ldg(topk_idx + static_cast<size_t>(t) * idx_stride + k) - local_offset;
       if (le >= 0 && le < E_local) {
 #pragma unroll
         for (int i = 0; i < E_GLOBAL / 32; ++i)
@@ -188,7 +188,8 @@ int launch_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, cuda
   if (p->T == 0) return B200MOE_OK;
   int grid = (ws->n_chunks + 3) / 4;
   const int* idx = p->routing_logits ? ws->topk_idx : p->topk_idx_in;
-  B200MOE_CUDA_TRY(launch_pdl(k_topk_bits, dim3(grid), dim3(128), 0, st, idx, p->T, p->local_expert_offset, p->E_local,
+  B200MOE_CUDA_TRY(launch_pdl(k_topk_bits, dim3(grid), dim3(128), 0, st, idx,
+                              p->topk_row_stride ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T, p->local_expert_offset, p->E_local,
                               ws->n_chunks, ws->chunk_bits));
   return B200MOE_OK;
 }

@@ -40,7 +40,8 @@ k_rank_scan(const uint32_t* __restrict__ chunk_bits, int n_chunks, int E_local, 
 
 // Padded layout (every CTA recomputes it in shared memory; CTA 0 publishes it) and the scatter, one warp per chunk.
 __global__ void __launch_bounds__(128)
-k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, const uint32_t* __restrict__ chunk_bits,
+k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, long long topk_stride,
+          const uint32_t* __restrict__ chunk_bits,
           const int* __restrict__ chunk_base, const int* __restrict__ counts, int T, int local_offset, int E_local,
           int n_chunks, int* __restrict__ block_offsets, int* __restrict__ total_blocks,
           int* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights, int* __restrict__ scatter_map) {
@@ -101,7 +102,7 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, co
   int dest[TOP_K];
 #pragma unroll
   for (int k = 0; k < TOP_K; ++k) {
-    int le = __ldg(topk_idx + static_cast<size_t>(t) * TOP_K + k) - local_offset;
+    int le = __ldg(topk_idx + static_cast<size_t>(t) * topk_stride + k) - local_offset;
     dest[k] = -1;
     if (le >= 0 && le < E_local) {
       uint32_t bits = __ldg(chunk_bits + static_cast<size_t>(chunk) * E_local + le);
@@ -109,7 +110,7 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, co
       int d = s_row_base[le] * BLOCK_M + rank;
       dest[k] = d;
       sorted_token_ids[d] = t;
-      sorted_weights[d] = __ldg(topk_w + static_cast<size_t>(t) * TOP_K + k);
+      sorted_weights[d] = __ldg(topk_w + static_cast<size_t>(t) * topk_stride + k);
     }
   }
   int4* out = reinterpret_cast<int4*>(scatter_map + static_cast<size_t>(t) * TOP_K);
@@ -120,7 +121,8 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, co
 // Copy the e4m3 row and the 56 scales of each real sorted row; pad rows are left as they are (their products are
 // never read).  One warp per row, grid-stride over the rows that exist.
 __global__ void __launch_bounds__(256)
-k_gather(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, int T,
+k_gather(const uint8_t* __restrict__ hidden, long long row_stride, const float* __restrict__ hidden_scale,
+         long long scale_token_stride, long long scale_block_stride, int T,
          const int* __restrict__ sorted_token_ids, const int* __restrict__ total_blocks, int R_max,
          uint8_t* __restrict__ a_sorted, float* __restrict__ a_scale_sorted) {
   const int lane = threadIdx.x & 31;
@@ -131,20 +133,22 @@ k_gather(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_sc
   for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
     int tok = __ldg(sorted_token_ids + r);
     if (tok >= T) continue;
-    const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * row_stride);
     uint4* dst = reinterpret_cast<uint4*>(a_sorted + static_cast<size_t>(r) * H);
 #pragma unroll
     for (int i = 0; i < H / 16 / 32; ++i) dst[i * 32 + lane] = __ldg(src + i * 32 + lane);
     for (int kb = lane; kb < H_BLOCKS; kb += 32)
-      a_scale_sorted[static_cast<size_t>(kb) * R_max + r] = __ldg(hidden_scale + static_cast<size_t>(kb) * T + tok);
+      a_scale_sorted[static_cast<size_t>(kb) * R_max + r] =
+          __ldg(hidden_scale + static_cast<size_t>(kb) * scale_block_stride + static_cast<size_t>(tok) * scale_token_stride);
   }
 }
 
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
-// Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).
+// Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
+// (the expert-parallel combine adds rows that are already weighted).
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
-         int T, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+         long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
   const int t = blockIdx.x;
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
@@ -152,7 +156,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   pdl_wait();
   if (threadIdx.x < TOP_K) {
     s_pos[threadIdx.x] = __ldg(scatter_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
-    s_w[threadIdx.x] = __ldg(topk_w + static_cast<size_t>(t) * TOP_K + threadIdx.x);
+    s_w[threadIdx.x] = topk_w ? __ldg(topk_w + static_cast<size_t>(t) * w_stride + threadIdx.x) : 1.0f;
   }
   __syncthreads();
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
@@ -188,6 +192,18 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   }
 }
 
+// Entry points for the expert-parallel code (ep.cu), which ranks (token, destination) pairs with the same scan and adds
+// returned rows with the same reduce.
+int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* counts, cudaStream_t st) {
+  B200MOE_CUDA_TRY(launch_pdl(k_rank_scan, dim3((E + 31) / 32), dim3(1024), 0, st, bits, n_chunks, E, base, counts));
+  return B200MOE_OK;
+}
+int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
+                              static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr)));
+  return B200MOE_OK;
+}
+
 int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   const int* idx = p->routing_logits ? ws->topk_idx : p->topk_idx_in;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
@@ -197,11 +213,12 @@ int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStrea
     B200MOE_CUDA_TRY(cudaMemsetAsync(ws->counts, 0, sizeof(int) * p->E_local, st));
     return B200MOE_OK;
   }
+  const long long tstride = (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : TOP_K;
   int scan_grid = (p->E_local + 31) / 32;
   B200MOE_CUDA_TRY(launch_pdl(k_rank_scan, dim3(scan_grid), dim3(1024), 0, st, ws->chunk_bits, ws->n_chunks, p->E_local,
                               ws->chunk_base, ws->counts));
   int grid = (ws->n_chunks + 3) / 4;
-  B200MOE_CUDA_TRY(launch_pdl(k_scatter, dim3(grid), dim3(128), 0, st, idx, w, ws->chunk_bits, ws->chunk_base,
+  B200MOE_CUDA_TRY(launch_pdl(k_scatter, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits, ws->chunk_base,
                               ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks, ws->block_offsets,
                               ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights, ws->scatter_map));
   return B200MOE_OK;
@@ -213,7 +230,10 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
   int grid = static_cast<int>((max_rows + 7) / 8);
   if (grid > num_sms * 8) grid = num_sms * 8;
   if (grid < 1) grid = 1;
-  B200MOE_CUDA_TRY(launch_pdl(k_gather, dim3(grid), dim3(256), 0, st, p->hidden_states, p->hidden_states_scale, p->T,
+  B200MOE_CUDA_TRY(launch_pdl(k_gather, dim3(grid), dim3(256), 0, st, p->hidden_states,
+                              p->hidden_row_stride ? p->hidden_row_stride : static_cast<long long>(H),
+                              p->hidden_states_scale, p->scale_token_stride ? p->scale_token_stride : 1LL,
+                              p->scale_block_stride ? p->scale_block_stride : static_cast<long long>(p->T), p->T,
                               ws->sorted_token_ids, ws->total_blocks, ws->R_max, ws->a_sorted, ws->a_scale_sorted));
   return B200MOE_OK;
 }
@@ -221,7 +241,8 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
 int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
-  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w, p->T,
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
+                              (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
                               p->output, p->output_f32));
   return B200MOE_OK;
 }

@@ -11,9 +11,10 @@ The reference is single-GPU: its only hook for sharding is ``local_expert_offset
      ITS experts only), giving one partial row per received token, already weighted and summed over its experts;
   4. combine: fp32 partial rows return to the token's home rank, which adds them and rounds once to bf16.
 
-Collectives are two ``all_to_all_single`` per direction (split sizes, then payload) over NCCL (NVLink/NVSwitch); payloads
-land in local HBM before any kernel reads them.  Routing and the expert path are injected callables, so the same
-plumbing runs on CPU ranks (gloo) in the tests with the CPU oracle standing in for the CUDA library.
+Collectives go over NCCL (NVLink/NVSwitch); payloads land in local HBM before any kernel reads them.  Two classes share
+the protocol: ``ExpertParallelMoE`` does the plumbing with torch ops around injected routing / expert callables, so it
+also runs on CPU ranks (gloo) in the tests with the CPU oracle standing in; ``CudaExpertParallelMoE`` is the B200 shard,
+where ranking, packing, the local experts and the final add are kernels of libb200moe.so.
 """
 from __future__ import annotations
 
@@ -136,19 +137,94 @@ class ExpertParallelMoE:
         return output
 
 
-def make_cuda_shard(weights: dict, rank: int, world: int, group=None) -> ExpertParallelMoE:
+class CudaExpertParallelMoE:
+    """One rank's shard on a B200, everything on the device done by libb200moe.so: routing, the stable ranking of
+    (token, destination) pairs and record packing (``b200moe_ep_dispatch``), the local experts reading the received
+    records in place (``kernel_from_records``) and the final add (``b200moe_ep_combine``).  torch.distributed only moves
+    bytes: one all_gather of the G x G record counts (read back to the host, which NCCL needs for the split sizes) and
+    one all_to_all_single per direction."""
+
+    def __init__(self, weights: dict, rank: int, world: int, group=None):
+        if E_GLOBAL % world:
+            raise ValueError(f"world size {world} does not divide {E_GLOBAL} experts")
+        self.weights, self.rank, self.world, self.group = weights, rank, world, group
+        self.e_local = E_GLOBAL // world
+        self.local_expert_offset = rank * self.e_local
+        self._buf = {}
+        self.last_records = None   # records this rank received in the last call (uint8 [n, 7456])
+        self.last_splits = None    # (send_splits, recv_splits) of the last call
+
+    def _buffers(self, T: int, device):
+        import ctypes as C
+        from . import _lib
+        key = (T, device.index)
+        b = self._buf.get(key)
+        if b is None:
+            n = C.c_size_t(0)
+            _lib.check(_lib.load().b200moe_ep_scratch_bytes(T, self.world, C.byref(n)), "b200moe_ep_scratch_bytes")
+            cap = T * min(TOP_K, self.world)
+            b = dict(scratch=torch.empty(max(n.value, 256), dtype=torch.uint8, device=device), scratch_bytes=n.value,
+                     send=torch.empty((max(cap, 1), ROW_BYTES), dtype=torch.uint8, device=device),
+                     counts=torch.zeros(self.world, dtype=torch.int32, device=device),
+                     slot_map=torch.empty((max(T, 1), TOP_K), dtype=torch.int32, device=device),
+                     all_counts=torch.empty(self.world * self.world, dtype=torch.int32, device=device))
+            self._buf = {key: b}
+        return b
+
+    @torch.no_grad()
+    def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor,
+                output: Optional[torch.Tensor] = None) -> torch.Tensor:
+        import ctypes as C
+        from . import _lib
+        from . import kernel as K
+        lib = _lib.load()
+        T = routing_logits.shape[0]
+        device = hidden_states.device
+        if output is None:
+            output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        idx, w = K.route(routing_logits, routing_bias, routed_scaling_factor)
+        b = self._buffers(T, device)
+        hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
+        hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _lib.check(lib.b200moe_ep_dispatch(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(), T,
+                                               self.world, b["scratch"].data_ptr(), b["scratch_bytes"],
+                                               b["send"].data_ptr(), b["counts"].data_ptr(), b["slot_map"].data_ptr(),
+                                               stream), "b200moe_ep_dispatch")
+        if self.world > 1:
+            dist.all_gather_into_tensor(b["all_counts"], b["counts"], group=self.group)
+            m = b["all_counts"].cpu().view(self.world, self.world)
+        else:
+            m = b["counts"].cpu().view(1, 1)
+        send_splits, recv_splits = m[self.rank].tolist(), m[:, self.rank].tolist()
+        n_send, n_recv = sum(send_splits), sum(recv_splits)
+        send = b["send"][:n_send]
+        if self.world > 1:
+            recv = torch.empty((n_recv, ROW_BYTES), dtype=torch.uint8, device=device)
+            dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
+        else:
+            recv = send
+        self.last_records, self.last_splits = recv, (send_splits, recv_splits)
+        wts = self.weights
+        part = K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
+                                     wts["gemm2_weights_scale"], self.local_expert_offset)
+        if self.world > 1:
+            back = torch.empty((n_send, H), dtype=torch.float32, device=device)
+            dist.all_to_all_single(back, part, send_splits, recv_splits, group=self.group)
+        else:
+            back = part
+        if T > 0:
+            with torch.cuda.device(device):
+                stream = torch.cuda.current_stream(device).cuda_stream
+                if n_send == 0:
+                    output.zero_()
+                else:
+                    _lib.check(lib.b200moe_ep_combine(back.data_ptr(), b["slot_map"].data_ptr(), T, output.data_ptr(),
+                                                      stream), "b200moe_ep_combine")
+        return output
+
+
+def make_cuda_shard(weights: dict, rank: int, world: int, group=None) -> CudaExpertParallelMoE:
     """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts)."""
-    from . import kernel as K
-
-    e_local = E_GLOBAL // world
-    offset = rank * e_local
-
-    def route_fn(logits, bias, scale):
-        return K.route(logits, bias, scale)
-
-    def expert_fn(idx, w, hs, scales):
-        return K.kernel_from_topk(idx, w, hs, scales, weights["gemm1_weights"], weights["gemm1_weights_scale"],
-                                  weights["gemm2_weights"], weights["gemm2_weights_scale"], offset,
-                                  out_dtype=torch.float32)
-
-    return ExpertParallelMoE(route_fn, expert_fn, rank, world, group)
+    return CudaExpertParallelMoE(weights, rank, world, group)

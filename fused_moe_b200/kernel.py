@@ -239,6 +239,45 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
 
 
 @torch.no_grad()
+def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                        local_expert_offset, output=None):
+    """The layer over expert-parallel dispatch records read in place: ``records`` is uint8 [n, 7456] in the layout of
+    ``b200moe_ep_dispatch`` (activations | 56 scales | 8 expert ids | 8 weights per row).  Returns float32 [n, 7168]
+    partial rows (sum over THIS shard's experts), in record order.  No reference counterpart."""
+    if not torch.is_tensor(records) or records.dim() != 2 or records.shape[1] != _lib.EP_RECORD_BYTES:
+        raise ValueError(f"records must be uint8 [n, {_lib.EP_RECORD_BYTES}]")
+    if records.dtype != torch.uint8 or not records.is_contiguous():
+        raise TypeError("records must be a contiguous uint8 tensor")
+    n = int(records.shape[0])
+    E_local, w13, w13s, w2, w2s = _check_weights(None, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                                                 gemm2_weights_scale)
+    _require_cuda(records=records, gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2,
+                  gemm2_weights_scale=w2s)
+    offset = _host_scalar(local_expert_offset, int)
+    if offset < 0 or offset + E_local > E_GLOBAL:
+        raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")
+    device = records.device
+    if output is None:
+        output = torch.empty((n, H), dtype=torch.float32, device=device)
+    elif output.dtype != torch.float32 or tuple(output.shape) != (n, H) or not output.is_contiguous():
+        raise ValueError("output must be a contiguous float32 tensor of shape [n, 7168]")
+    if n == 0:
+        return output
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        stream_ptr = torch.cuda.current_stream(device).cuda_stream
+        ws = _workspace(device, n, E_local, stream_ptr)
+        p = _lib.Problem()
+        _lib.check(lib.b200moe_ep_record_layout(records.data_ptr(), n, C.byref(p)), "b200moe_ep_record_layout")
+        p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
+        p.gemm1_weights, p.gemm1_weights_scale = w13.data_ptr(), w13s.data_ptr()
+        p.gemm2_weights, p.gemm2_weights_scale = w2.data_ptr(), w2s.data_ptr()
+        p.output, p.output_f32 = None, output.data_ptr()
+        _lib.check(lib.b200moe_forward(C.byref(p), C.byref(ws.struct), stream_ptr), "b200moe_forward")
+    return output
+
+
+@torch.no_grad()
 def route(routing_logits, routing_bias, routed_scaling_factor):
     """Routing stage alone -> (topk_idx int32 [T,8], topk_weights float32 [T,8]); experts in descending biased score,
     ties to the lower id (reference: solution/python/pure_triton_impl.py:96-190).  Used by expert-parallel ranks, which

@@ -82,6 +82,12 @@ typedef struct b200moe_problem {
   const int32_t* topk_idx_in;
   const float* topk_w_in;
   float* output_f32; /* optional [T,7168] float32: if non-NULL the un-rounded sums go here and `output` may be NULL */
+  /* Optional strides, 0 = the dense layouts above.  They let the layer read token rows in place from an
+   * expert-parallel receive buffer (b200moe_ep_dispatch row format) instead of from four separate tensors. */
+  int64_t hidden_row_stride;  /* bytes between token rows of hidden_states (0 = 7168) */
+  int64_t scale_token_stride; /* floats between tokens in hidden_states_scale (0 = 1) */
+  int64_t scale_block_stride; /* floats between 128-column blocks in hidden_states_scale (0 = T) */
+  int64_t topk_row_stride;    /* elements between tokens in topk_idx_in / topk_w_in (0 = 8) */
 } b200moe_problem;
 
 /* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
@@ -184,6 +190,26 @@ int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* 
 int b200moe_sort_static(const int32_t* topk_idx, const float* topk_w, int32_t T, int32_t E_local,
                         int32_t local_expert_offset, int32_t* counts, int32_t* block_offsets, int32_t* total_blocks,
                         int32_t* sorted_token_ids, float* sorted_weights, int32_t* scatter_map, void* stream);
+
+/* ---- Expert parallelism (no reference counterpart: the reference is single-GPU) -------------------------------------
+ * A token row travels once to every rank that owns at least one of its eight experts, as one 7456-byte record:
+ *   [0,7168) e4m3 activations | [7168,7392) 56 float32 scales | [7392,7424) 8 int32 expert ids | [7424,7456) 8 float32
+ *   weights.
+ * b200moe_ep_dispatch ranks the (token, destination) pairs (stable: by destination rank, then token id), writes the
+ * records into `send_rows` in that order, the number of records per destination into `send_counts[world]` and, for
+ * each of the token's eight experts, the record index its destination uses into `slot_map[T,8]` (-1 for an expert whose
+ * rank already got the token through an earlier expert).  The receiver runs b200moe_forward on the records in place
+ * (routing_logits = NULL, the four strides of b200moe_problem set by b200moe_ep_record_layout) and returns float32 rows
+ * in the same order; b200moe_ep_combine adds the rows of each token and writes bfloat16.
+ * `scratch` needs b200moe_ep_scratch_bytes(T, world) bytes; send_rows holds up to T * min(8, world) records. */
+#define B200MOE_EP_RECORD_BYTES 7456
+int b200moe_ep_scratch_bytes(int32_t T, int32_t world, size_t* bytes /* host */);
+int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                        const float* hidden_states_scale, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
+                        uint8_t* send_rows, int32_t* send_counts, int32_t* slot_map, void* stream);
+/* Fills the pointer and stride fields of `p` for `n` records at `records` (p->T is set to n). */
+int b200moe_ep_record_layout(const uint8_t* records, int32_t n, b200moe_problem* p /* host */);
+int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output, void* stream);
 
 /* Synchronises `stream`, copies the device status word to *status (host) and clears it.
  * Returns B200MOE_EDEVICE if it was non-zero.  No reference counterpart (the reference has no device-side waits). */

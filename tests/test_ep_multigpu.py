@@ -45,7 +45,7 @@ def _worker(rank, world, port, ret):
         ref = total[sl].bfloat16().float()
         err = (out.float() - ref).abs()
         tol = 1e-2 + 2e-2 * ref.abs()
-        ret[rank] = (float((err / tol).max()), pairs, shard.last_plan.send_splits, shard.last_plan.recv_splits,
+        ret[rank] = (float((err / tol).max()), pairs, shard.last_splits[0], shard.last_splits[1],
                      bool(torch.isfinite(out.float()).all()))
     finally:
         dist.destroy_process_group()
