@@ -272,7 +272,9 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
             "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale", "local_expert_offset",
             "routed_scaling_factor")
     pos = [inp[k] for k in keys]
-    launches_per_step = 7
+    # our kernels per step: route, rank-scan, scatter, gather, GEMM1, GEMM2, reduce; under expert parallelism the
+    # dispatch adds dest-bits, rank-scan, slots, pack, the receiver swaps route for chunk-bits, combine adds one
+    launches_per_step = 7 if world == 1 else 13
     if world == 1:
         def step():
             K.kernel(*pos, out)
@@ -353,7 +355,12 @@ def run_ours(args):
         roof = dict(bound="hbm", achieved=wbytes / (g1_us * 1e-6) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s")
         roof["peak_note"] = f"{peaks['source']} copy bandwidth"
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update(kernel="k_grouped_gemm<1> (GEMM1+SwiGLU)", kernel_us=g1_us, traffic=None,
+    # DRAM traffic: ncu on the T=4096 case (profiles/gemm_grouped_fp8_prefill4096_e32.md) measured 1.09 x the
+    # algorithmic bytes (weights once, activations mostly from L2); the full-size launch is too large to capture, so
+    # its traffic is that ratio times its own algorithmic bytes
+    alg_bytes = rec["active_experts"] * (2 * I * H) + pairs_rank * (H + 2 * I + 4 * 16)
+    roof.update(kernel="k_grouped_gemm<1> (GEMM1+SwiGLU)", kernel_us=g1_us, traffic=int(1.09 * alg_bytes),
+                traffic_note="1.09 x algorithmic bytes, ratio from the ncu capture of the T=4096 case",
                 algorithmic=f"{pairs_rank} pairs x 58,720,256 flop; {rec['active_experts']} experts x 29,360,128 B + pairs x 7168 B")
 
     sweep = []
