@@ -1,7 +1,7 @@
 """Benchmark of the fused MoE layer: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
 
 One "step" = one pass of the layer over one batch of seeded synthetic tokens (fused_moe_b200.synth).  The headline
-workload is the prefill configuration: T = 16384 global tokens, skewed router, all 256 experts sharded over the N
+workload is the prefill configuration: T = 16384 global tokens, N(0,1) router logits (the base distribution), all 256 experts sharded over the N
 GPUs (256/N local experts per GPU, tokens split evenly, expert-parallel dispatch/combine for N > 1), so the N = 1, 2,
 4, 8 lines describe the same global problem ("strong" scaling).  `--workload` selects the other configurations
 (decode T=1, small batch T=80, prefill with the reference's 32-local-expert shape); a short sweep over them is added
@@ -37,7 +37,7 @@ WEIGHT_BYTES_PER_EXPERT = 2 * I * H + H * I
 
 WORKLOADS = {
     # name: (T_global, local experts at N=1, skewed router)
-    "prefill_ep": (16384, 256, True),
+    "prefill_ep": (16384, 256, False),
     "prefill_e32": (16384, 32, True),
     "prefill4096_e32": (4096, 32, True),
     "small_e32": (80, 32, False),
@@ -318,6 +318,10 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     if world == 1:
         st, pairs, active, blocks = stage_times(K, inp, T_loc, E_local, offset)
     else:
+        shard.profile = True
+        step()
+        rec["ep_phase_us"] = {k: round(v, 1) for k, v in shard.phase_times().items()}
+        shard.profile = False
         recs = shard.last_records
         st, pairs, active, blocks = stage_times(K, inp, recs.shape[0], E_local, offset, records=recs)
     rec.update(stage_us=st, pairs=pairs, active_experts=active, row_blocks=blocks)
@@ -395,13 +399,13 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: T={T_global} global tokens, {rec['E_local']} local experts/GPU of 256, "
-                                   f"hidden 7168, intermediate 2048, top-8, skewed router" ,
+                                   f"hidden 7168, intermediate 2048, top-8, {'skewed' if skew else 'N(0,1)'} router logits",
                        "parallelism": f"ep{world}", "l2": "inputs_exceed_l2 (expert weights >> 126 MB)",
                        "pairs_rank0": rec["pairs"], "active_experts_rank0": rec["active_experts"]},
             "e2e": rec["e2e"], "gpu_launches": rec["launches_per_step"] * rec["steps"],
             "clocks": rec.get("clocks"), "roofline": roof, "stage_us": {k: round(v, 1) for k, v in rec["stage_us"].items()},
             "layer_roofline": {"bound": lr["bound"], "frac": round(lr["frac"], 4), "t_roof_us": round(lr["t_roof_us"], 1)},
-            "cpu_baseline": cpu, "sweep": sweep,
+            "ep_phase_us_rank0": rec.get("ep_phase_us"), "cpu_baseline": cpu, "sweep": sweep,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -153,6 +153,22 @@ class CudaExpertParallelMoE:
         self._buf = {}
         self.last_records = None   # records this rank received in the last call (uint8 [n, 7456])
         self.last_splits = None    # (send_splits, recv_splits) of the last call
+        self.profile = False       # True: record CUDA events around each phase, read them with phase_times()
+        self._events = []
+
+    def _mark(self, name):
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._events.append((name, ev))
+
+    def phase_times(self):
+        """us per phase of the last profiled call (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for (_, a), (name, b) in zip(self._events[:-1], self._events[1:]):
+            out[name] = a.elapsed_time(b) * 1e3
+        return out
 
     def _buffers(self, T: int, device):
         import ctypes as C
@@ -182,7 +198,10 @@ class CudaExpertParallelMoE:
         device = hidden_states.device
         if output is None:
             output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        self._events = []
+        self._mark("start")
         idx, w = K.route(routing_logits, routing_bias, routed_scaling_factor)
+        self._mark("route")
         b = self._buffers(T, device)
         hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
         hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
@@ -192,6 +211,7 @@ class CudaExpertParallelMoE:
                                                self.world, b["scratch"].data_ptr(), b["scratch_bytes"],
                                                b["send"].data_ptr(), b["counts"].data_ptr(), b["slot_map"].data_ptr(),
                                                stream), "b200moe_ep_dispatch")
+        self._mark("dispatch_kernels")
         if self.world > 1:
             dist.all_gather_into_tensor(b["all_counts"], b["counts"], group=self.group)
             m = b["all_counts"].cpu().view(self.world, self.world)
@@ -200,20 +220,24 @@ class CudaExpertParallelMoE:
         send_splits, recv_splits = m[self.rank].tolist(), m[:, self.rank].tolist()
         n_send, n_recv = sum(send_splits), sum(recv_splits)
         send = b["send"][:n_send]
+        self._mark("counts_exchange_and_host_read")
         if self.world > 1:
             recv = torch.empty((n_recv, ROW_BYTES), dtype=torch.uint8, device=device)
             dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
         else:
             recv = send
         self.last_records, self.last_splits = recv, (send_splits, recv_splits)
+        self._mark("all_to_all_records")
         wts = self.weights
         part = K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
                                      wts["gemm2_weights_scale"], self.local_expert_offset)
+        self._mark("local_experts")
         if self.world > 1:
             back = torch.empty((n_send, H), dtype=torch.float32, device=device)
             dist.all_to_all_single(back, part, send_splits, recv_splits, group=self.group)
         else:
             back = part
+        self._mark("all_to_all_partials")
         if T > 0:
             with torch.cuda.device(device):
                 stream = torch.cuda.current_stream(device).cuda_stream
@@ -222,6 +246,7 @@ class CudaExpertParallelMoE:
                 else:
                     _lib.check(lib.b200moe_ep_combine(back.data_ptr(), b["slot_map"].data_ptr(), T, output.data_ptr(),
                                                       stream), "b200moe_ep_combine")
+        self._mark("combine")
         return output
 
 
