@@ -338,6 +338,9 @@ def run_ours(args):
     device = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        # NCCL prints its version banner to stdout at NCCL_DEBUG=VERSION; stdout carries exactly one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     from fused_moe_b200 import kernel as K
     peaks = load_peaks()
