@@ -40,6 +40,20 @@ class Problem(C.Structure):
         ("scale_token_stride", C.c_int64),
         ("scale_block_stride", C.c_int64),
         ("topk_row_stride", C.c_int64),
+        ("out_seg_count", C.c_int32),
+        ("out_seg_start", C.c_int32 * 9),
+        ("out_seg_base", C.c_void_p * 8),
+    ]
+
+
+class EpPeers(C.Structure):
+    """Mirror of ``b200moe_ep_peers``."""
+
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("recv_records", C.c_void_p * 8),
+        ("flags", C.c_void_p * 8),
     ]
 
 
@@ -91,6 +105,11 @@ SYMBOLS = {
     "b200moe_ep_scratch_bytes": (C.c_int, (C.c_int32, C.c_int32, C.POINTER(C.c_size_t))),
     "b200moe_ep_dispatch": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.c_int32, C.c_void_p, C.c_size_t) + (C.c_void_p,) * 4),
     "b200moe_ep_record_layout": (C.c_int, (C.c_void_p, C.c_int32, C.POINTER(Problem))),
+    "b200moe_ep_rank": (C.c_int, (C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                  C.c_void_p)),
+    "b200moe_ep_pack_peers": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.POINTER(EpPeers), C.POINTER(C.c_int32),
+                                                           C.c_void_p, C.c_size_t, C.c_void_p)),
+    "b200moe_ep_barrier": (C.c_int, (C.POINTER(EpPeers), C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_ep_combine": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),
 }

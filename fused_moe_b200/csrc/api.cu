@@ -226,8 +226,10 @@ int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
-  if (p->T > 0 && ((!p->output && !p->output_f32) || !aligned16(p->output) || !aligned16(p->output_f32)))
+  if (p->T > 0 && p->out_seg_count == 0 &&
+      ((!p->output && !p->output_f32) || !aligned16(p->output) || !aligned16(p->output_f32)))
     return B200MOE_EINVAL;
+  if (p->out_seg_count < 0 || p->out_seg_count > 8) return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
   return launch_reduce(p, ws, static_cast<cudaStream_t>(stream));
@@ -238,7 +240,7 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   if (rc) return rc;
   if (p->T == 0) return B200MOE_OK;
   if (!p->hidden_states || !p->hidden_states_scale || !p->gemm1_weights || !p->gemm1_weights_scale ||
-      !p->gemm2_weights || !p->gemm2_weights_scale || (!p->output && !p->output_f32))
+      !p->gemm2_weights || !p->gemm2_weights_scale || (!p->output && !p->output_f32 && p->out_seg_count == 0))
     return B200MOE_EINVAL;
   if (!aligned16(p->hidden_states) || !aligned16(p->gemm1_weights) || !aligned16(p->gemm2_weights) ||
       !aligned16(p->output) || !aligned16(p->output_f32))
@@ -248,6 +250,10 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   } else if (!p->topk_idx_in || !p->topk_w_in) {
     return B200MOE_EINVAL;
   }
+  if (p->out_seg_count < 0 || p->out_seg_count > 8) return B200MOE_EINVAL;
+  for (int i = 0; i < p->out_seg_count; ++i)
+    if (!p->out_seg_base[i] || !aligned16(p->out_seg_base[i]) || p->out_seg_start[i] > p->out_seg_start[i + 1])
+      return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

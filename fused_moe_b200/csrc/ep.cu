@@ -118,20 +118,45 @@ k_dispatch_slots(const int* __restrict__ topk_idx, const uint32_t* __restrict__ 
   out[1] = make_int4(slot[4], slot[5], slot[6], slot[7]);
 }
 
-// One warp per record.
+// Where records go when they are written straight into the destinations' memory: segment d (records for rank d)
+// starts at row row0[d] of base[d].
+struct PeerTargets {
+  uint8_t* base[8];
+  int row0[8];
+};
+
+// One warp per record.  With send_rows the records form one local buffer in slot order; with send_rows == nullptr
+// (world <= 8) each record is stored into its destination rank's receive buffer, which may be another GPU's memory.
 __global__ void __launch_bounds__(256)
 k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale,
                const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int T, const int* __restrict__ counts,
-               int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows) {
+               int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows, const PeerTargets peers) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   pdl_launch_dependents();
   pdl_wait();
   int total = 0;
-  for (int d = 0; d < world; ++d) total += __ldg(counts + d);
+  int seg[9];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) {
+    seg[d] = total;
+    if (d < world) total += __ldg(counts + d);
+  }
+  seg[8] = total;
+  if (world > 8)
+    for (int d = 8; d < world; ++d) total += __ldg(counts + d);
   for (int s = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); s < total; s += gridDim.x * warps_per_cta) {
     const int tok = __ldg(slot_token + s);
-    uint8_t* rec = send_rows + static_cast<size_t>(s) * EP_RECORD;
+    uint8_t* rec;
+    if (send_rows) {
+      rec = send_rows + static_cast<size_t>(s) * EP_RECORD;
+    } else {
+      int d = 0;
+#pragma unroll
+      for (int j = 1; j < 8; ++j)
+        if (s >= seg[j]) d = j;
+      rec = peers.base[d] + static_cast<size_t>(peers.row0[d] + (s - seg[d])) * EP_RECORD;
+    }
     const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
     uint4* dst = reinterpret_cast<uint4*>(rec);
 #pragma unroll
@@ -144,6 +169,38 @@ k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hid
           __ldg(topk_w + static_cast<size_t>(tok) * TOP_K + lane);
     }
   }
+  if (!send_rows) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
+}
+
+// Bounded all-rank barrier on flags mapped into every rank: publish `epoch`, then wait for everybody's.
+constexpr int ST_BARRIER_TIMEOUT = 2;
+__global__ void __launch_bounds__(32)
+k_ep_barrier(const PeerTargets flags /* base[r] = rank r's int flags[world] */, int world, int rank, int epoch,
+             int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x;
+  __threadfence_system();
+  if (lane < world) {
+    volatile int* remote = reinterpret_cast<volatile int*>(flags.base[lane]) + rank;
+    *remote = epoch;
+  }
+  __threadfence_system();
+  if (lane < world) {
+    volatile int* mine = reinterpret_cast<volatile int*>(flags.base[rank]) + lane;
+    const long long t0 = clock64();
+    while (*mine < epoch) {
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (atomicCAS(status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
+          status[1] = rank;
+          status[2] = lane;
+          status[3] = epoch;
+        }
+        break;
+      }
+    }
+  }
+  __threadfence_system();
 }
 
 }  // namespace b200moe
@@ -162,11 +219,47 @@ int b200moe_ep_scratch_bytes(int32_t T, int32_t world, size_t* bytes) {
   return B200MOE_OK;
 }
 
-int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
-                        const float* hidden_states_scale, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
-                        uint8_t* send_rows, int32_t* send_counts, int32_t* slot_map, void* stream) {
+namespace {
+struct Scratch {
+  uint32_t* bits;
+  int* cbase;
+  int* counts;
+  int* slot_token;
+};
+Scratch carve_scratch(void* scratch, int T, int world) {
+  const size_t n_chunks = (static_cast<size_t>(T) + 31) / 32;
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  Scratch s;
+  s.bits = reinterpret_cast<uint32_t*>(base);
+  s.cbase = reinterpret_cast<int*>(base + up(4 * n_chunks * world));
+  s.counts = reinterpret_cast<int*>(base + 2 * up(4 * n_chunks * world));
+  s.slot_token = reinterpret_cast<int*>(base + 2 * up(4 * n_chunks * world) + up(4 * static_cast<size_t>(world)));
+  return s;
+}
+int check_scratch(int32_t T, int32_t world, const void* scratch, size_t scratch_bytes) {
   size_t need = 0;
   int rc = b200moe_ep_scratch_bytes(T, world, &need);
+  if (rc) return rc;
+  if (T > 0 && (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u)))
+    return B200MOE_EWORKSPACE;
+  return B200MOE_OK;
+}
+int launch_pack(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                const float* hidden_states_scale, int32_t T, int32_t world, const Scratch& sc, uint8_t* send_rows,
+                const PeerTargets& peers, cudaStream_t st) {
+  long long max_pairs = static_cast<long long>(T) * (world < TOP_K ? world : TOP_K);
+  int pgrid = static_cast<int>((max_pairs + 7) / 8);
+  if (pgrid > 148 * 8) pgrid = 148 * 8;
+  B200MOE_CUDA_TRY(launch_pdl(k_pack_records, dim3(pgrid), dim3(256), 0, st, hidden_states, hidden_states_scale,
+                              topk_idx, topk_w, T, sc.counts, world, sc.slot_token, send_rows, peers));
+  return B200MOE_OK;
+}
+}  // namespace
+
+int b200moe_ep_rank(const int32_t* topk_idx, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
+                    int32_t* send_counts, int32_t* slot_map, void* stream) {
+  int rc = check_scratch(T, world, scratch, scratch_bytes);
   if (rc) return rc;
   if (!send_counts) return B200MOE_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -174,31 +267,60 @@ int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint
     B200MOE_CUDA_TRY(cudaMemsetAsync(send_counts, 0, sizeof(int32_t) * world, st));
     return B200MOE_OK;
   }
-  if (!topk_idx || !topk_w || !hidden_states || !hidden_states_scale || !scratch || !send_rows || !slot_map)
-    return B200MOE_EINVAL;
-  if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255u)) return B200MOE_EWORKSPACE;
-  if ((reinterpret_cast<uintptr_t>(send_rows) & 15u) || (reinterpret_cast<uintptr_t>(hidden_states) & 15u) ||
-      (reinterpret_cast<uintptr_t>(slot_map) & 15u))
-    return B200MOE_EINVAL;
+  if (!topk_idx || !slot_map || (reinterpret_cast<uintptr_t>(slot_map) & 15u)) return B200MOE_EINVAL;
+  const Scratch sc = carve_scratch(scratch, T, world);
   const int n_chunks = (T + 31) / 32;
-  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-  uint8_t* base = static_cast<uint8_t*>(scratch);
-  uint32_t* bits = reinterpret_cast<uint32_t*>(base);
-  int* cbase = reinterpret_cast<int*>(base + up(4 * static_cast<size_t>(n_chunks) * world));
-  int* counts = reinterpret_cast<int*>(base + 2 * up(4 * static_cast<size_t>(n_chunks) * world));
-  int* slot_token = reinterpret_cast<int*>(base + 2 * up(4 * static_cast<size_t>(n_chunks) * world) +
-                                           up(4 * static_cast<size_t>(world)));
   const int epr = E_GLOBAL / world;
   const int grid = (n_chunks + 3) / 4;
-  B200MOE_CUDA_TRY(launch_pdl(k_dest_bits, dim3(grid), dim3(128), 0, st, topk_idx, T, epr, world, n_chunks, bits));
-  if ((rc = launch_rank_scan(bits, n_chunks, world, cbase, counts, st))) return rc;
-  B200MOE_CUDA_TRY(launch_pdl(k_dispatch_slots, dim3(grid), dim3(128), 0, st, topk_idx, bits, cbase, counts, T, epr,
-                              world, n_chunks, send_counts, slot_token, slot_map));
-  long long max_pairs = static_cast<long long>(T) * (world < TOP_K ? world : TOP_K);
-  int pgrid = static_cast<int>((max_pairs + 7) / 8);
-  if (pgrid > 148 * 8) pgrid = 148 * 8;
-  B200MOE_CUDA_TRY(launch_pdl(k_pack_records, dim3(pgrid), dim3(256), 0, st, hidden_states, hidden_states_scale,
-                              topk_idx, topk_w, T, counts, world, slot_token, send_rows));
+  B200MOE_CUDA_TRY(launch_pdl(k_dest_bits, dim3(grid), dim3(128), 0, st, topk_idx, T, epr, world, n_chunks, sc.bits));
+  if ((rc = launch_rank_scan(sc.bits, n_chunks, world, sc.cbase, sc.counts, st))) return rc;
+  B200MOE_CUDA_TRY(launch_pdl(k_dispatch_slots, dim3(grid), dim3(128), 0, st, topk_idx, sc.bits, sc.cbase, sc.counts, T,
+                              epr, world, n_chunks, send_counts, sc.slot_token, slot_map));
+  return B200MOE_OK;
+}
+
+int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                        const float* hidden_states_scale, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
+                        uint8_t* send_rows, int32_t* send_counts, int32_t* slot_map, void* stream) {
+  int rc = b200moe_ep_rank(topk_idx, T, world, scratch, scratch_bytes, send_counts, slot_map, stream);
+  if (rc || T == 0) return rc;
+  if (!topk_w || !hidden_states || !hidden_states_scale || !send_rows) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(send_rows) & 15u) || (reinterpret_cast<uintptr_t>(hidden_states) & 15u))
+    return B200MOE_EINVAL;
+  PeerTargets none = {};
+  return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, world, carve_scratch(scratch, T, world),
+                     send_rows, none, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                          const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers,
+                          const int32_t* dst_row0, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!peers || !dst_row0 || peers->world < 1 || peers->world > 8) return B200MOE_EINVAL;
+  int rc = check_scratch(T, peers->world, scratch, scratch_bytes);
+  if (rc || T == 0) return rc;
+  if (!topk_idx || !topk_w || !hidden_states || !hidden_states_scale) return B200MOE_EINVAL;
+  if (reinterpret_cast<uintptr_t>(hidden_states) & 15u) return B200MOE_EINVAL;
+  PeerTargets tg = {};
+  for (int d = 0; d < peers->world; ++d) {
+    if (!peers->recv_records[d] || (reinterpret_cast<uintptr_t>(peers->recv_records[d]) & 15u) || dst_row0[d] < 0)
+      return B200MOE_EINVAL;
+    tg.base[d] = peers->recv_records[d];
+    tg.row0[d] = dst_row0[d];
+  }
+  return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, peers->world,
+                     carve_scratch(scratch, T, peers->world), nullptr, tg, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_barrier(const b200moe_ep_peers* peers, int32_t epoch, int32_t* status, void* stream) {
+  if (!peers || !status || peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world)
+    return B200MOE_EINVAL;
+  PeerTargets fl = {};
+  for (int d = 0; d < peers->world; ++d) {
+    if (!peers->flags[d]) return B200MOE_EINVAL;
+    fl.base[d] = reinterpret_cast<uint8_t*>(peers->flags[d]);
+  }
+  B200MOE_CUDA_TRY(launch_pdl(k_ep_barrier, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), fl, peers->world,
+                              peers->rank, epoch, status));
   return B200MOE_OK;
 }
 

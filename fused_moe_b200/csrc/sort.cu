@@ -143,13 +143,29 @@ k_gather(const uint8_t* __restrict__ hidden, long long row_stride, const float* 
   }
 }
 
+struct OutSegments {
+  int count;
+  int start[9];
+  float* base[8];
+};
+
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
 // Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
 // (the expert-parallel combine adds rows that are already weighted).
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
-         long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+         long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs) {
   const int t = blockIdx.x;
+  float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr;
+  if (segs.count > 0) {
+    // rows of segment i go to segs.base[i], which may be memory of another GPU (plain 16-byte stores)
+    int i = 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+      if (j < segs.count && t >= segs.start[j]) i = j;
+    out = nullptr;
+    dst_row = segs.base[i] + static_cast<size_t>(t - segs.start[i]) * H;
+  }
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
   pdl_launch_dependents();
@@ -184,12 +200,13 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       }
       reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    if (out_f32) {
-      float4* dst = reinterpret_cast<float4*>(out_f32 + static_cast<size_t>(t) * H) + 2 * v;
+    if (dst_row) {
+      float4* dst = reinterpret_cast<float4*>(dst_row) + 2 * v;
       dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
       dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
+  if (segs.count > 0) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
 }
 
 // Entry points for the expert-parallel code (ep.cu), which ranks (token, destination) pairs with the same scan and adds
@@ -199,8 +216,9 @@ int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* 
   return B200MOE_OK;
 }
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
+  OutSegments none = {};
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
-                              static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr)));
+                              static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none));
   return B200MOE_OK;
 }
 
@@ -241,9 +259,13 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
 int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
+  OutSegments segs = {};
+  segs.count = p->out_seg_count;
+  for (int i = 0; i < 8; ++i) segs.base[i] = p->out_seg_base[i];
+  for (int i = 0; i < 9; ++i) segs.start[i] = p->out_seg_start[i];
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
-                              p->output, p->output_f32));
+                              p->output, p->output_f32, segs));
   return B200MOE_OK;
 }
 

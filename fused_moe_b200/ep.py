@@ -144,10 +144,19 @@ class CudaExpertParallelMoE:
     bytes: one all_gather of the G x G record counts (read back to the host, which NCCL needs for the split sizes) and
     one all_to_all_single per direction."""
 
-    def __init__(self, weights: dict, rank: int, world: int, group=None):
+    def __init__(self, weights: dict, rank: int, world: int, group=None, transport: str = "auto"):
+        """transport: "peer" — records and partial rows are stored straight into the destination GPU's memory by the
+        pack and reduce kernels (torch symmetric memory supplies the mapped buffers; up to 8 GPUs of one node), with a
+        bounded flag barrier between phases and no payload collective; "nccl" — two all_to_all_single; "auto" — peer
+        when it can be set up, else nccl."""
         if E_GLOBAL % world:
             raise ValueError(f"world size {world} does not divide {E_GLOBAL} experts")
+        if transport not in ("auto", "peer", "nccl"):
+            raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
         self.weights, self.rank, self.world, self.group = weights, rank, world, group
+        self.transport = "nccl" if (world == 1 or world > 8) else transport
+        self._peer = None          # symmetric-memory state of the peer transport
+        self._epoch = 0
         self.e_local = E_GLOBAL // world
         self.local_expert_offset = rank * self.e_local
         self._buf = {}
@@ -169,6 +178,55 @@ class CudaExpertParallelMoE:
         for (_, a), (name, b) in zip(self._events[:-1], self._events[1:]):
             out[name] = a.elapsed_time(b) * 1e3
         return out
+
+    def _peer_setup(self, T: int, device):
+        """Maps one slab per rank into every rank: [flags | receive records | returned partial rows].  Collective."""
+        import ctypes as C
+        import os
+        from . import _lib
+        if self._peer is not None and self._peer["T"] >= T:
+            return self._peer
+        # plain peer mappings only: no NVLink multicast object is bound to these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        cap_recv = self.world * T                      # every token of every rank may come here
+        cap_back = T * min(TOP_K, self.world)          # one returned row per (token, destination)
+        off_recv = 256
+        off_back = off_recv + (cap_recv * ROW_BYTES + 255) // 256 * 256
+        total = off_back + cap_back * H * 4
+        slab = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        slab[:256].zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(slab, group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        peers = _lib.EpPeers()
+        peers.world, peers.rank = self.world, self.rank
+        for r in range(self.world):
+            peers.flags[r] = ptrs[r]
+            peers.recv_records[r] = ptrs[r] + off_recv
+        status = torch.zeros(4, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)                 # flags are zero everywhere before the first epoch
+        self._peer = dict(T=T, slab=slab, hdl=hdl, ptrs=ptrs, peers=peers, off_recv=off_recv, off_back=off_back,
+                          cap_recv=cap_recv, cap_back=cap_back, status=status)
+        return self._peer
+
+    def check_status(self):
+        """Raises if a bounded peer barrier ran out since the last check (synchronises)."""
+        if self._peer is None:
+            return
+        st = self._peer["status"].cpu().tolist()
+        if st[0] != 0:
+            self._peer["status"].zero_()
+            raise RuntimeError(f"expert-parallel barrier timed out: code={st[0]} rank={st[1]} waiting_for={st[2]} "
+                               f"epoch={st[3]}")
+
+    def _barrier(self, stream):
+        import ctypes as C
+        from . import _lib
+        self._epoch += 1
+        _lib.check(_lib.load().b200moe_ep_barrier(C.byref(self._peer["peers"]), self._epoch,
+                                                  self._peer["status"].data_ptr(), stream), "b200moe_ep_barrier")
 
     def _buffers(self, T: int, device):
         import ctypes as C
@@ -202,6 +260,16 @@ class CudaExpertParallelMoE:
         self._mark("start")
         idx, w = K.route(routing_logits, routing_bias, routed_scaling_factor)
         self._mark("route")
+        if self.transport in ("auto", "peer"):
+            try:
+                self._peer_setup(T, device)
+                self.transport = "peer"
+            except Exception:
+                if self.transport == "peer":
+                    raise
+                self.transport = "nccl"   # symmetric memory is not available here: fall back to the collective path
+        if self.transport == "peer":
+            return self._forward_peer(idx, w, hidden_states, hidden_states_scale, output, T, device)
         b = self._buffers(T, device)
         hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
         hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
@@ -250,6 +318,62 @@ class CudaExpertParallelMoE:
         return output
 
 
-def make_cuda_shard(weights: dict, rank: int, world: int, group=None) -> CudaExpertParallelMoE:
+    def _forward_peer(self, idx, w, hidden_states, hidden_states_scale, output, T, device):
+        import ctypes as C
+        from . import _lib
+        from . import kernel as K
+        lib = _lib.load()
+        pr = self._peer
+        b = self._buffers(T, device)
+        hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
+        hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _lib.check(lib.b200moe_ep_rank(idx.data_ptr(), T, self.world, b["scratch"].data_ptr(), b["scratch_bytes"],
+                                           b["counts"].data_ptr(), b["slot_map"].data_ptr(), stream),
+                       "b200moe_ep_rank")
+            self._mark("dispatch_kernels")
+            dist.all_gather_into_tensor(b["all_counts"], b["counts"], group=self.group)
+            m = b["all_counts"].cpu().view(self.world, self.world)   # m[s][d] = records s sends to d
+            self._mark("counts_exchange_and_host_read")
+            me = self.rank
+            send_splits, recv_splits = m[me].tolist(), m[:, me].tolist()
+            n_send, n_recv = sum(send_splits), sum(recv_splits)
+            self.last_splits = (send_splits, recv_splits)
+            # my segment in rank d's receive buffer starts after the segments of the ranks before me
+            row0 = (C.c_int32 * self.world)(*[int(m[:me, d].sum()) for d in range(self.world)])
+            _lib.check(lib.b200moe_ep_pack_peers(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(), T,
+                                                 C.byref(pr["peers"]), row0, b["scratch"].data_ptr(),
+                                                 b["scratch_bytes"], stream), "b200moe_ep_pack_peers")
+            self._barrier(stream)
+            self._mark("records_to_peers")
+            recv = pr["slab"][pr["off_recv"]:pr["off_recv"] + n_recv * ROW_BYTES].view(n_recv, ROW_BYTES)
+            self.last_records = recv
+            # rows received from source s return to s's slab, after the rows s sent to the ranks before me
+            starts, bases, acc = [0], [], 0
+            for s_rank in range(self.world):
+                acc += recv_splits[s_rank]
+                starts.append(acc)
+                bases.append(pr["ptrs"][s_rank] + pr["off_back"] + int(m[s_rank, :me].sum()) * H * 4)
+            wts = self.weights
+            K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
+                                  wts["gemm2_weights_scale"], self.local_expert_offset, out_segments=(starts, bases))
+            self._mark("local_experts_and_rows_to_peers")
+            self._barrier(stream)
+            self._mark("barrier")
+            if output is None:
+                output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+            if T > 0:
+                if n_send == 0:
+                    output.zero_()
+                else:
+                    back_ptr = pr["ptrs"][me] + pr["off_back"]
+                    _lib.check(lib.b200moe_ep_combine(back_ptr, b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
+                               "b200moe_ep_combine")
+            self._mark("combine")
+        return output
+
+
+def make_cuda_shard(weights: dict, rank: int, world: int, group=None, transport: str = "auto") -> CudaExpertParallelMoE:
     """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts)."""
-    return CudaExpertParallelMoE(weights, rank, world, group)
+    return CudaExpertParallelMoE(weights, rank, world, group, transport)

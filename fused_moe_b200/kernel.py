@@ -240,10 +240,12 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
 
 @torch.no_grad()
 def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
-                        local_expert_offset, output=None):
+                        local_expert_offset, output=None, out_segments=None):
     """The layer over expert-parallel dispatch records read in place: ``records`` is uint8 [n, 7456] in the layout of
     ``b200moe_ep_dispatch`` (activations | 56 scales | 8 expert ids | 8 weights per row).  Returns float32 [n, 7168]
-    partial rows (sum over THIS shard's experts), in record order.  No reference counterpart."""
+    partial rows (sum over THIS shard's experts), in record order.  With ``out_segments = (starts, bases)`` — row
+    ranges ``starts[i]..starts[i+1]`` and raw float32 device addresses ``bases[i]`` (at most 8, possibly peer-GPU
+    memory) — the rows are stored there instead and nothing is returned.  No reference counterpart."""
     if not torch.is_tensor(records) or records.dim() != 2 or records.shape[1] != _lib.EP_RECORD_BYTES:
         raise ValueError(f"records must be uint8 [n, {_lib.EP_RECORD_BYTES}]")
     if records.dtype != torch.uint8 or not records.is_contiguous():
@@ -257,7 +259,12 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
     if offset < 0 or offset + E_local > E_GLOBAL:
         raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")
     device = records.device
-    if output is None:
+    if out_segments is not None:
+        starts, bases = out_segments
+        if len(bases) > 8 or len(starts) != len(bases) + 1 or starts[0] != 0 or starts[-1] != n:
+            raise ValueError("out_segments must cover rows 0..n with at most 8 segments")
+        output = None
+    elif output is None:
         output = torch.empty((n, H), dtype=torch.float32, device=device)
     elif output.dtype != torch.float32 or tuple(output.shape) != (n, H) or not output.is_contiguous():
         raise ValueError("output must be a contiguous float32 tensor of shape [n, 7168]")
@@ -272,7 +279,15 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
         p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
         p.gemm1_weights, p.gemm1_weights_scale = w13.data_ptr(), w13s.data_ptr()
         p.gemm2_weights, p.gemm2_weights_scale = w2.data_ptr(), w2s.data_ptr()
-        p.output, p.output_f32 = None, output.data_ptr()
+        if out_segments is None:
+            p.output, p.output_f32 = None, output.data_ptr()
+        else:
+            p.output, p.output_f32 = None, None
+            p.out_seg_count = len(bases)
+            for i, (s0, b) in enumerate(zip(starts, bases)):
+                p.out_seg_start[i] = int(s0)
+                p.out_seg_base[i] = int(b)
+            p.out_seg_start[len(bases)] = int(starts[-1])
         _lib.check(lib.b200moe_forward(C.byref(p), C.byref(ws.struct), stream_ptr), "b200moe_forward")
     return output
 

@@ -88,6 +88,13 @@ typedef struct b200moe_problem {
   int64_t scale_token_stride; /* floats between tokens in hidden_states_scale (0 = 1) */
   int64_t scale_block_stride; /* floats between 128-column blocks in hidden_states_scale (0 = T) */
   int64_t topk_row_stride;    /* elements between tokens in topk_idx_in / topk_w_in (0 = 8) */
+  /* Optional segmented float32 output (expert-parallel receiver writing straight into its peers' memory): rows
+   * [out_seg_start[i], out_seg_start[i+1]) of the result go to out_seg_base[i] + (row - out_seg_start[i]) * 7168.
+   * out_seg_count = 0 disables it; when set, `output` and `output_f32` are ignored.  The bases may be peer-GPU
+   * addresses (plain stores over NVLink; no TMA and no multicast touch them). */
+  int32_t out_seg_count;
+  int32_t out_seg_start[9];
+  float* out_seg_base[8];
 } b200moe_problem;
 
 /* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
@@ -209,6 +216,26 @@ int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint
                         uint8_t* send_rows, int32_t* send_counts, int32_t* slot_map, void* stream);
 /* Fills the pointer and stride fields of `p` for `n` records at `records` (p->T is set to n). */
 int b200moe_ep_record_layout(const uint8_t* records, int32_t n, b200moe_problem* p /* host */);
+/* Peer-memory variant for up to 8 GPUs of one node (buffers mapped into every rank, e.g. torch symmetric memory):
+ * b200moe_ep_rank does the ranking only (send_counts, slot_map, and the record order kept in `scratch`);
+ * b200moe_ep_pack_peers then writes each record directly into its destination's receive buffer —
+ * record j of the segment for rank d goes to recv_records[d] + (dst_row0[d] + j) * 7456 — so dispatch needs no
+ * collective for the payload.  b200moe_ep_barrier is a bounded all-rank barrier on a small flag array in the same
+ * mapped memory: every rank stores `epoch` into flags[rank] of every peer and waits (about 2 s at most) until its own
+ * copy shows `epoch` from everybody; on a timeout it records B200MOE status code 2 in `status` and returns. */
+typedef struct b200moe_ep_peers {
+  int32_t world;
+  int32_t rank;
+  uint8_t* recv_records[8];
+  int32_t* flags[8];
+} b200moe_ep_peers;
+int b200moe_ep_rank(const int32_t* topk_idx, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
+                    int32_t* send_counts, int32_t* slot_map, void* stream);
+int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                          const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers /* host */,
+                          const int32_t* dst_row0 /* host, [world] */, void* scratch, size_t scratch_bytes,
+                          void* stream);
+int b200moe_ep_barrier(const b200moe_ep_peers* peers /* host */, int32_t epoch, int32_t* status, void* stream);
 int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output, void* stream);
 
 /* Synchronises `stream`, copies the device status word to *status (host) and clears it.

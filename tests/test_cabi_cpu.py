@@ -29,10 +29,11 @@ def test_header_symbols_exported(lib):
 
 def test_struct_mirrors_match_header():
     header = (ROOT / "include" / "b200moe.h").read_text()
-    for cls, cname in ((_lib.Problem, "b200moe_problem"), (_lib.Workspace, "b200moe_workspace")):
+    for cls, cname in ((_lib.Problem, "b200moe_problem"), (_lib.Workspace, "b200moe_workspace"),
+                       (_lib.EpPeers, "b200moe_ep_peers")):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-        names = re.findall(r"(\w+)\s*;", body)
+        names = re.findall(r"(\w+)\s*(?:\[\d+\])?;", body)
         assert names == [f[0] for f in cls._fields_]
 
 

@@ -30,11 +30,17 @@ def _worker(rank, world, port, ret):
         inp = synth.make_inputs(T_GLOBAL, e_l, seed=23, local_expert_offset=rank * e_l, skew=True, device=dev)
         t_loc = T_GLOBAL // world
         sl = slice(rank * t_loc, (rank + 1) * t_loc)
-        shard = ep.make_cuda_shard(inp, rank, world)
-        out = shard.forward(inp["routing_logits"][sl].contiguous(), inp["routing_bias"],
-                            inp["hidden_states"][sl].contiguous(), inp["hidden_states_scale"][:, sl].contiguous(),
-                            inp["routed_scaling_factor"])
+        args = (inp["routing_logits"][sl].contiguous(), inp["routing_bias"], inp["hidden_states"][sl].contiguous(),
+                inp["hidden_states_scale"][:, sl].contiguous(), inp["routed_scaling_factor"])
+        # collective transport, then the peer-memory transport (records and partial rows stored straight into the
+        # other GPU), twice: the second call reuses the mapped buffers
+        out_nccl = ep.make_cuda_shard(inp, rank, world, transport="nccl").forward(*args)
+        shard = ep.make_cuda_shard(inp, rank, world, transport="peer")
+        out = shard.forward(*args)
+        out2 = shard.forward(*args)
         K.check_status()
+        shard.check_status()
+        same = bool(torch.equal(out, out_nccl) and torch.equal(out, out2))
         # reference: every rank evaluates ITS experts for ALL tokens on the CPU, partial sums are added over ranks
         idx, w = oracle.route(inp["routing_logits"], inp["routing_bias"], inp["routed_scaling_factor"])
         part32, _, pairs = oracle.forward_from_topk(idx, w, inp["hidden_states"], inp["hidden_states_scale"],
@@ -46,7 +52,7 @@ def _worker(rank, world, port, ret):
         err = (out.float() - ref).abs()
         tol = 1e-2 + 2e-2 * ref.abs()
         ret[rank] = (float((err / tol).max()), pairs, shard.last_splits[0], shard.last_splits[1],
-                     bool(torch.isfinite(out.float()).all()))
+                     bool(torch.isfinite(out.float()).all()) and same)
     finally:
         dist.destroy_process_group()
 
