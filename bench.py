@@ -321,6 +321,8 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
         shard.profile = True
         step()
         rec["ep_phase_us"] = {k: round(v, 1) for k, v in shard.phase_times().items()}
+        rec["ep_transport"] = shard.transport
+        shard.check_status()
         shard.profile = False
         recs = shard.last_records
         st, pairs, active, blocks = stage_times(K, inp, recs.shape[0], E_local, offset, records=recs)
@@ -403,7 +405,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: T={T_global} global tokens, {rec['E_local']} local experts/GPU of 256, "
                                    f"hidden 7168, intermediate 2048, top-8, {'skewed' if skew else 'N(0,1)'} router logits",
-                       "parallelism": f"ep{world}", "l2": "inputs_exceed_l2 (expert weights >> 126 MB)",
+                       "parallelism": f"ep{world}", "ep_transport": rec.get("ep_transport"), "l2": "inputs_exceed_l2 (expert weights >> 126 MB)",
                        "pairs_rank0": rec["pairs"], "active_experts_rank0": rec["active_experts"]},
             "e2e": rec["e2e"], "gpu_launches": rec["launches_per_step"] * rec["steps"],
             "clocks": rec.get("clocks"), "roofline": roof, "stage_us": {k: round(v, 1) for k, v in rec["stage_us"].items()},
