@@ -334,14 +334,14 @@ class CudaExpertParallelMoE:
                        "b200moe_ep_rank")
             self._mark("dispatch_kernels")
             dist.all_gather_into_tensor(b["all_counts"], b["counts"], group=self.group)
-            m = b["all_counts"].cpu().view(self.world, self.world)   # m[s][d] = records s sends to d
+            m = b["all_counts"].cpu().view(self.world, self.world).tolist()   # m[s][d] = records s sends to d
             self._mark("counts_exchange_and_host_read")
             me = self.rank
-            send_splits, recv_splits = m[me].tolist(), m[:, me].tolist()
+            send_splits, recv_splits = m[me], [m[s_rank][me] for s_rank in range(self.world)]
             n_send, n_recv = sum(send_splits), sum(recv_splits)
             self.last_splits = (send_splits, recv_splits)
             # my segment in rank d's receive buffer starts after the segments of the ranks before me
-            row0 = (C.c_int32 * self.world)(*[int(m[:me, d].sum()) for d in range(self.world)])
+            row0 = (C.c_int32 * self.world)(*[sum(m[s_rank][d] for s_rank in range(me)) for d in range(self.world)])
             _lib.check(lib.b200moe_ep_pack_peers(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(), T,
                                                  C.byref(pr["peers"]), row0, b["scratch"].data_ptr(),
                                                  b["scratch_bytes"], stream), "b200moe_ep_pack_peers")
@@ -354,7 +354,7 @@ class CudaExpertParallelMoE:
             for s_rank in range(self.world):
                 acc += recv_splits[s_rank]
                 starts.append(acc)
-                bases.append(pr["ptrs"][s_rank] + pr["off_back"] + int(m[s_rank, :me].sum()) * H * 4)
+                bases.append(pr["ptrs"][s_rank] + pr["off_back"] + sum(m[s_rank][:me]) * H * 4)
             wts = self.weights
             K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
                                   wts["gemm2_weights_scale"], self.local_expert_offset, out_segments=(starts, bases))
