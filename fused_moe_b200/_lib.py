@@ -14,6 +14,7 @@ LIB_PATH = PKG_DIR / "libb200moe.so"
 OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3, -4, -5, -6
 SORT_STATIC_MAX_ENTRIES = 32768
 EP_RECORD_BYTES = 7456
+DECODE_MAX_T = 2
 
 
 class Problem(C.Structure):
@@ -101,6 +102,8 @@ SYMBOLS = {
     "b200moe_gemm1": (C.c_int, _PW),
     "b200moe_gemm2": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),
+    "b200moe_gemv1": (C.c_int, _PW),
+    "b200moe_gemv2": (C.c_int, _PW),
     "b200moe_sort_static": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32) + (C.c_void_p,) * 7),
     "b200moe_ep_scratch_bytes": (C.c_int, (C.c_int32, C.c_int32, C.POINTER(C.c_size_t))),
     "b200moe_ep_dispatch": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.c_int32, C.c_void_p, C.c_size_t) + (C.c_void_p,) * 4),

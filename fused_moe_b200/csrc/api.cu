@@ -21,6 +21,8 @@ int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStr
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
+int launch_gemv1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
+int launch_gemv2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 
 struct DeviceInfo {
   int checked = 0;  // 0 unknown, 1 ok, -1 unsupported
@@ -223,6 +225,30 @@ int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
   return launch_gemm2(p, ws, sms, static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_gemv1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  int rc = check_problem(p, ws);
+  if (rc) return rc;
+  if (p->T > B200MOE_DECODE_MAX_T) return B200MOE_EINVAL;
+  if (p->T > 0 && (!p->hidden_states || !p->hidden_states_scale || !p->gemm1_weights || !p->gemm1_weights_scale ||
+                   !aligned16(p->hidden_states) || !aligned16(p->gemm1_weights)))
+    return B200MOE_EINVAL;
+  int sms;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_gemv1(p, ws, sms, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_gemv2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  int rc = check_problem(p, ws);
+  if (rc) return rc;
+  if (p->T > B200MOE_DECODE_MAX_T) return B200MOE_EINVAL;
+  if (p->T > 0 && (!p->gemm2_weights || !p->gemm2_weights_scale || !aligned16(p->gemm2_weights) ||
+                   (!p->output && !p->output_f32)))
+    return B200MOE_EINVAL;
+  int sms;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_gemv2(p, ws, sms, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
@@ -257,6 +283,13 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   int sms;
   if ((rc = device_info(&sms))) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->routing_logits && p->T <= B200MOE_DECODE_MAX_T && p->out_seg_count == 0 && !p->hidden_row_stride &&
+      !p->scale_token_stride && !p->scale_block_stride) {
+    // decode: a few tokens, one or two rows per expert — stream the weights through matrix-vector kernels
+    if ((rc = launch_route(p, ws, st))) return rc;
+    if ((rc = launch_gemv1(p, ws, sms, st))) return rc;
+    return launch_gemv2(p, ws, sms, st);
+  }
   if (p->routing_logits) {
     if ((rc = launch_route(p, ws, st))) return rc;
   } else {

@@ -36,6 +36,7 @@ extern "C" {
 #define B200MOE_TOPK_GROUP 4
 #define B200MOE_QBLOCK 128
 #define B200MOE_BLOCK_M 128 /* rows per expert tile; every expert segment is padded to a multiple of this */
+#define B200MOE_DECODE_MAX_T 2 /* up to this many tokens b200moe_forward takes the matrix-vector (decode) path */
 
 enum {
   B200MOE_OK = 0,
@@ -146,7 +147,8 @@ int b200moe_workspace_carve(void* base, size_t bytes, int32_t T, int32_t E_local
 int b200moe_workspace_init(const b200moe_workspace* ws /* host */, void* stream);
 
 /* Whole layer: route -> rank -> scatter -> gather -> GEMM1+SwiGLU -> GEMM2 -> weighted reduce, all on `stream`,
- * no host synchronisation.  Replaces solution/python/pure_triton_impl.py:2125-2403 (kernel), :2025-2123 (_kernel_t1),
+ * no host synchronisation.  With routing_logits given and T <= B200MOE_DECODE_MAX_T it runs route -> GEMV1+SwiGLU ->
+ * GEMV2+reduce instead (b200moe_gemv1 / b200moe_gemv2 below): no sort, no gather, fp32 intermediate.  Replaces solution/python/pure_triton_impl.py:2125-2403 (kernel), :2025-2123 (_kernel_t1),
  * solution/python/triton_impl.py:346-566 and solution/python/triton_impl_t901.py:40-185. */
 int b200moe_forward(const b200moe_problem* p /* host */, const b200moe_workspace* ws /* host */, void* stream);
 
@@ -175,6 +177,12 @@ int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* s
  * Replaces _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196) and the CuTe GEMM2
  * (solution/python/cute_gemm2_mma.py:250-304). */
 int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* Decode path stages (need topk_idx / topk_w of b200moe_route in the workspace; the fp32 intermediate [T*8, 2048] is
+ * kept in the workspace's expert_out array): one warp per output element streams the weight rows from HBM.
+ * Replaces the reference's T = 1 path: GEMM1 with BLOCK_M = 16 (solution/python/pure_triton_impl.py:1824-1940) and
+ * _t1_fused_gemm2_reduce_kernel (solution/python/pure_triton_impl.py:1676-1750). */
+int b200moe_gemv1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+int b200moe_gemv2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
 /* out[t] = sum_k topk_w[t,k] * expert_out[scatter_map[t,k]], fp32 accumulate, bf16 (and/or fp32) store, no atomics.
  * Replaces _token_reduce_kernel (solution/python/pure_triton_impl.py:1758-1821) and
  * _token_reduce_weighted_kernel (solution/python/triton_impl.py:163-207). */

@@ -68,7 +68,14 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     assert torch.equal(idx, ref["topk_idx"]), "expert ids differ from the oracle"
     assert torch.equal(w, ref["topk_w"]), "routing weights differ from the oracle"
 
-    # sort metadata: bit-exact
+    # sort metadata: bit-exact.  The decode path (T <= 2) does not sort, so the stage is run here explicitly.
+    from fused_moe_b200 import _lib
+    from fused_moe_b200.kernel import _problem
+    p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]), inp["routing_logits"], inp["routing_bias"],
+                 inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"],
+                 inp["gemm2_weights"], inp["gemm2_weights_scale"], out)
+    _lib.check(_lib.load().b200moe_sort(C.byref(p), C.byref(ws.struct), torch.cuda.current_stream().cuda_stream), "sort")
+    torch.cuda.synchronize()
     s = oracle.sort(ref["topk_idx"], ref["topk_w"], E_local, offset)
     tb = int(ws.view("total_blocks", torch.int32, (1,)).item())
     assert tb == s["total_blocks"]
@@ -85,7 +92,8 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
 
 @pytest.mark.parametrize("T,E_local,seed,offset,skew", [
     (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration
-    (1, 32, 5, 96, False),     # decode
+    (1, 32, 5, 96, False),     # decode path (matrix-vector kernels)
+    (2, 32, 9, 0, False),      # decode path, two tokens
     (80, 32, 1, 0, False),     # small batch
     (33, 8, 3, 60, False),     # E_local below one warp, non-zero offset, two token chunks
     (40, 3, 13, 253, True),    # last experts, skewed router
