@@ -111,6 +111,9 @@ struct __align__(8) GemmAux {
   int grp[E_GLOBAL + 1];
   int cnt[E_GLOBAL];
   float amax[2][2][BLOCK_M];
+  // GEMM2 epilogue: per promotion warp, 32 rows x 16 columns (+4 padding: conflict-free 16-byte accesses) through which
+  // the thread-per-row accumulators are turned into stores of 64 contiguous bytes per row
+  float out_stage[NUM_PROMO_WARPS][32][20];
 };
 
 template <int MODE, int CG>
@@ -421,32 +424,67 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         amax = fmaxf(ex[r_in_tile], ex[BLOCK_M + r_in_tile]);
         const float s = fmaxf(amax, 1e-20f) * (1.0f / 448.0f);
         const float inv = 1.0f / s;
-        if (valid) {
-          uint8_t* q1p = args.inter_q + static_cast<size_t>(row) * I + ti.nt * 128 + h * 64;
-          uint8_t* q2p = q1p + static_cast<size_t>(args.R_max) * I;
+        // Quantise in registers (thread = row), then pass each term's 32 rows x 64 bytes through shared memory so that a
+        // store instruction writes 64 contiguous bytes of 8 rows instead of 16 bytes of 32 rows.
+        uint4 t1[4], t2[4];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t w1[4], w2[4];
+        for (int v = 0; v < 4; ++v) {
+          uint32_t w1[4], w2[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int j = v * 16 + u * 4;
-              w1[u] = pack4_e4m3(ACC(j) * inv, ACC(j + 1) * inv, ACC(j + 2) * inv, ACC(j + 3) * inv);
-              float back[4];
-              unpack4_e4m3(w1[u], back);
-              w2[u] = pack4_e4m3((ACC(j) - back[0] * s) * inv, (ACC(j + 1) - back[1] * s) * inv,
-                                 (ACC(j + 2) - back[2] * s) * inv, (ACC(j + 3) - back[3] * s) * inv);
-            }
-            reinterpret_cast<uint4*>(q1p)[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-            reinterpret_cast<uint4*>(q2p)[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+          for (int u = 0; u < 4; ++u) {
+            const int j = v * 16 + u * 4;
+            w1[u] = pack4_e4m3(ACC(j) * inv, ACC(j + 1) * inv, ACC(j + 2) * inv, ACC(j + 3) * inv);
+            float back[4];
+            unpack4_e4m3(w1[u], back);
+            w2[u] = pack4_e4m3((ACC(j) - back[0] * s) * inv, (ACC(j + 1) - back[1] * s) * inv,
+                               (ACC(j + 2) - back[2] * s) * inv, (ACC(j + 3) - back[3] * s) * inv);
           }
-          if (h == 0) args.inter_scale[static_cast<size_t>(ti.nt) * args.R_max + row] = s;
+          t1[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+          t2[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
         }
-      } else {
-        if (valid) {
-          float* op = args.expert_out + static_cast<size_t>(row) * H + ti.nt * TILE_N + h * 128;
+        float (*stg)[20] = aux->out_stage[warp];   // 80-byte row pitch: 64 bytes used
+        const int rows_valid = ti.cnt - ti.m_local * BLOCK_M - q * 32;
+        uint8_t* qbase = args.inter_q + static_cast<size_t>(ti.mblk * BLOCK_M + q * 32) * I + ti.nt * 128 + h * 64;
+        const int rsub = lane >> 2, csub = lane & 3;
 #pragma unroll
-          for (int v = 0; v < 32; ++v)
-            reinterpret_cast<float4*>(op)[v] = make_float4(ACC(4 * v), ACC(4 * v + 1), ACC(4 * v + 2), ACC(4 * v + 3));
+        for (int term = 0; term < 2; ++term) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(&stg[lane][4 * v]) = term == 0 ? t1[v] : t2[v];
+          __syncwarp();
+          uint8_t* dst = qbase + (term == 0 ? 0 : static_cast<size_t>(args.R_max) * I);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int r = rsub + 8 * j;
+            const uint4 val = *reinterpret_cast<const uint4*>(&stg[r][4 * csub]);
+            if (r < rows_valid) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * I + csub * 16) = val;
+          }
+          __syncwarp();
+        }
+        if (valid && h == 0) args.inter_scale[static_cast<size_t>(ti.nt) * args.R_max + row] = s;
+      } else {
+        // Thread-per-row stores would touch 32 rows with 16 bytes each per instruction.  Instead each warp passes its
+        // 32 x 128 block through shared memory 16 columns at a time and stores 64 contiguous bytes per row (8 rows per
+        // instruction), which halves the sectors L2 has to merge.
+        float (*stg)[20] = aux->out_stage[warp];
+        const int rows_valid = ti.cnt - ti.m_local * BLOCK_M - q * 32;   // valid rows of this warp's 32 (may be <= 0)
+        float* obase = args.expert_out + static_cast<size_t>(ti.mblk * BLOCK_M + q * 32) * H + ti.nt * TILE_N + h * 128;
+        const int rsub = lane >> 2, csub = (lane & 3) * 4;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            *reinterpret_cast<float4*>(&stg[lane][4 * v]) =
+                make_float4(ACC(piece * 16 + 4 * v), ACC(piece * 16 + 4 * v + 1), ACC(piece * 16 + 4 * v + 2),
+                            ACC(piece * 16 + 4 * v + 3));
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int r = rsub + 8 * j;
+            const float4 val = *reinterpret_cast<const float4*>(&stg[r][csub]);
+            if (r < rows_valid)
+              *reinterpret_cast<float4*>(obase + static_cast<size_t>(r) * H + piece * 16 + csub) = val;
+          }
+          __syncwarp();
         }
       }
     }
