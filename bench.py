@@ -202,6 +202,8 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
     res = {}
     if records is None and T <= _lib.DECODE_MAX_T:
         names = ("route", "gemv1", "gemv2")          # decode path of b200moe_forward
+    elif records is None and T <= _lib.PROLOGUE_MAX_T:
+        names = ("prologue_small", "gemm1", "gemm2", "reduce")   # route + sort + gather are one launch here
     else:
         names = ("topk_bits" if records is not None else "route", "sort", "gather", "gemm1", "gemm2", "reduce")
     for name in names:
@@ -215,7 +217,7 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
         e1.record()
         torch.cuda.synchronize()
         res[name] = e0.elapsed_time(e1) * 1e3 / reps
-    if "sort" not in names:
+    if "gemv1" in names:
         _lib.check(lib.b200moe_sort(C.byref(p), C.byref(ws.struct), stream), "sort")  # only for the pair statistics
         torch.cuda.synchronize()
     counts = ws.view("counts", torch.int32, (E_local,)).cpu()

@@ -15,6 +15,7 @@ OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3,
 SORT_STATIC_MAX_ENTRIES = 32768
 EP_RECORD_BYTES = 7456
 DECODE_MAX_T = 2
+PROLOGUE_MAX_T = 128
 
 
 class Problem(C.Structure):
@@ -99,6 +100,7 @@ SYMBOLS = {
     "b200moe_topk_bits": (C.c_int, _PW),
     "b200moe_sort": (C.c_int, _PW),
     "b200moe_gather": (C.c_int, _PW),
+    "b200moe_prologue_small": (C.c_int, _PW),
     "b200moe_gemm1": (C.c_int, _PW),
     "b200moe_gemm2": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),

@@ -16,6 +16,7 @@ int record_cuda_error(cudaError_t e) {
 
 int launch_route(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_topk_bits(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
+int launch_small_prologue(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_sort(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
@@ -205,6 +206,17 @@ int b200moe_gather(const b200moe_problem* p, const b200moe_workspace* ws, void* 
   return launch_gather(p, ws, sms, static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_prologue_small(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  int rc = check_problem(p, ws);
+  if (rc) return rc;
+  if (p->T > B200MOE_PROLOGUE_MAX_T) return B200MOE_ETOOLARGE;
+  if (p->hidden_row_stride || p->scale_token_stride || p->scale_block_stride) return B200MOE_EINVAL;
+  if (p->T > 0 && (!p->routing_logits || !p->routing_bias || !p->hidden_states || !p->hidden_states_scale ||
+                   !aligned16(p->hidden_states)))
+    return B200MOE_EINVAL;
+  return launch_small_prologue(p, ws, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
@@ -290,13 +302,18 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
     if ((rc = launch_gemv1(p, ws, sms, st))) return rc;
     return launch_gemv2(p, ws, sms, st);
   }
-  if (p->routing_logits) {
-    if ((rc = launch_route(p, ws, st))) return rc;
+  if (p->routing_logits && p->T <= B200MOE_PROLOGUE_MAX_T && !p->hidden_row_stride && !p->scale_token_stride && !p->scale_block_stride) {
+    // small batch: routing, ranking, layout, scatter and gather in one single-CTA kernel (same results)
+    if ((rc = launch_small_prologue(p, ws, st))) return rc;
   } else {
-    if ((rc = launch_topk_bits(p, ws, st))) return rc;
+    if (p->routing_logits) {
+      if ((rc = launch_route(p, ws, st))) return rc;
+    } else {
+      if ((rc = launch_topk_bits(p, ws, st))) return rc;
+    }
+    if ((rc = launch_sort(p, ws, st))) return rc;
+    if ((rc = launch_gather(p, ws, sms, st))) return rc;
   }
-  if ((rc = launch_sort(p, ws, st))) return rc;
-  if ((rc = launch_gather(p, ws, sms, st))) return rc;
   if ((rc = launch_gemm1(p, ws, sms, st))) return rc;
   if ((rc = launch_gemm2(p, ws, sms, st))) return rc;
   return launch_reduce(p, ws, st);

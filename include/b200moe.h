@@ -36,6 +36,7 @@ extern "C" {
 #define B200MOE_TOPK_GROUP 4
 #define B200MOE_QBLOCK 128
 #define B200MOE_BLOCK_M 128 /* rows per expert tile; every expert segment is padded to a multiple of this */
+#define B200MOE_PROLOGUE_MAX_T 128 /* largest batch of b200moe_prologue_small */
 #define B200MOE_DECODE_MAX_T 2 /* up to this many tokens b200moe_forward takes the matrix-vector (decode) path */
 
 enum {
@@ -169,6 +170,11 @@ int b200moe_sort(const b200moe_problem* p, const b200moe_workspace* ws, void* st
  * Replaces the in-kernel row gather of the reference GEMM1 (solution/python/pure_triton_impl.py:986-994) and
  * _dequantize_gemm1_sorted_a_kernel (solution/python/triton_impl.py:67-110), without the dequantisation. */
 int b200moe_gather(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* b200moe_route + b200moe_sort + b200moe_gather in ONE launch for batches of at most B200MOE_PROLOGUE_MAX_T tokens with
+ * dense inputs (all strides 0, routing_logits given); B200MOE_ETOOLARGE above that size, B200MOE_EINVAL for strided
+ * inputs.  Leaves exactly the same workspace contents as the three stages.  b200moe_forward uses it for such batches.
+ * Replaces, for such batches, the reference's routing + sort sequence (solution/python/pure_triton_impl.py:2207-2273). */
+int b200moe_prologue_small(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
 /* Grouped FP8 GEMM1 with fp32 block-scale promotion every 128 K, SwiGLU, two-term e4m3 re-quantisation.
  * Replaces _fused_moe_gemm1_swiglu_kernel (solution/python/pure_triton_impl.py:886-1046) and the CuTe GEMM1 chain
  * (solution/python/cute_gemm1_mma.py:247-289, solution/python/triton_impl.py:113-150). */
