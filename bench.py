@@ -206,6 +206,8 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
         names = ("prologue_small", "gemm1", "gemm2", "reduce")   # route + sort + gather are one launch here
     else:
         names = ("topk_bits" if records is not None else "route", "sort", "gather", "gemm1", "gemm2", "reduce")
+    if records is None and T <= _lib.SKINNY_MAX_T:   # the GEMM kernels b200moe_forward uses at this batch size
+        names = tuple(n + "_skinny" if n in ("gemm1", "gemm2") else n for n in names)
     for name in names:
         fn = getattr(lib, "b200moe_" + name)
         _lib.check(fn(C.byref(p), C.byref(ws.struct), stream), name)  # warm
@@ -216,7 +218,7 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
             fn(C.byref(p), C.byref(ws.struct), stream)
         e1.record()
         torch.cuda.synchronize()
-        res[name] = e0.elapsed_time(e1) * 1e3 / reps
+        res[name.replace("_skinny", "")] = e0.elapsed_time(e1) * 1e3 / reps
     if "gemv1" in names:
         _lib.check(lib.b200moe_sort(C.byref(p), C.byref(ws.struct), stream), "sort")  # only for the pair statistics
         torch.cuda.synchronize()

@@ -15,7 +15,8 @@ OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3,
 SORT_STATIC_MAX_ENTRIES = 32768
 EP_RECORD_BYTES = 7456
 DECODE_MAX_T = 2
-PROLOGUE_MAX_T = 128
+PROLOGUE_MAX_T = 32
+SKINNY_MAX_T = 256
 
 
 class Problem(C.Structure):
@@ -83,6 +84,8 @@ class Workspace(C.Structure):
         ("inter_q", C.c_void_p),
         ("inter_scale", C.c_void_p),
         ("expert_out", C.c_void_p),
+        ("gemm_tile_ctr", C.c_void_p),
+        ("gemm_partial", C.c_void_p),
     ]
 
 
@@ -101,6 +104,8 @@ SYMBOLS = {
     "b200moe_sort": (C.c_int, _PW),
     "b200moe_gather": (C.c_int, _PW),
     "b200moe_prologue_small": (C.c_int, _PW),
+    "b200moe_gemm1_skinny": (C.c_int, _PW),
+    "b200moe_gemm2_skinny": (C.c_int, _PW),
     "b200moe_gemm1": (C.c_int, _PW),
     "b200moe_gemm2": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),

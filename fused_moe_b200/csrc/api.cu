@@ -21,6 +21,8 @@ int launch_sort(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
+int launch_gemm1_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
+int launch_gemm2_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gemv1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemv2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
@@ -55,6 +57,9 @@ static int r_max_for(int T, int E) {
   return static_cast<int>(blocks * BLOCK_M);
 }
 
+// Token-minor GEMM tiles: at most R_max / 64 sub-blocks of sorted rows x 28 n-tiles (GEMM2; GEMM1 has 16).
+static size_t tile_ctr_count(size_t r_max) { return r_max / 64 * 28; }
+
 // Walks the workspace layout; with base == nullptr only the total is computed.
 static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
   const size_t R = static_cast<size_t>(r_max_for(T, E));
@@ -81,6 +86,8 @@ static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
   uint8_t* inter_q = take(2 * R * I);
   uint8_t* inter_scale = take(sizeof(float) * I_BLOCKS * R);
   uint8_t* expert_out = take(sizeof(float) * R * H);
+  uint8_t* gemm_tile_ctr = take(sizeof(int32_t) * tile_ctr_count(R));
+  uint8_t* gemm_partial = take(sizeof(float) * B200MOE_GEMM_MAX_CTAS * 2 * (2 * 64 * 128));
   if (w) {
     w->T = T;
     w->E_local = E;
@@ -102,6 +109,8 @@ static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
     w->inter_q = inter_q;
     w->inter_scale = reinterpret_cast<float*>(inter_scale);
     w->expert_out = reinterpret_cast<float*>(expert_out);
+    w->gemm_tile_ctr = reinterpret_cast<int32_t*>(gemm_tile_ctr);
+    w->gemm_partial = reinterpret_cast<float*>(gemm_partial);
   }
   return off;
 }
@@ -167,6 +176,9 @@ int b200moe_workspace_carve(void* base, size_t bytes, int32_t T, int32_t E_local
 int b200moe_workspace_init(const b200moe_workspace* ws, void* stream) {
   if (!ws || !ws->status) return B200MOE_EINVAL;
   B200MOE_CUDA_TRY(cudaMemsetAsync(ws->status, 0, sizeof(int32_t) * 4, static_cast<cudaStream_t>(stream)));
+  if (ws->gemm_tile_ctr)
+    B200MOE_CUDA_TRY(cudaMemsetAsync(ws->gemm_tile_ctr, 0, sizeof(int32_t) * tile_ctr_count(ws->R_max),
+                                     static_cast<cudaStream_t>(stream)));
   return B200MOE_OK;
 }
 
@@ -235,6 +247,26 @@ int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
   int sms;
   if ((rc = device_info(&sms))) return rc;
   return launch_gemm2(p, ws, sms, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  int rc = check_problem(p, ws);
+  if (rc) return rc;
+  if (p->T > 0 && (!p->gemm1_weights || !p->gemm1_weights_scale || !aligned16(p->gemm1_weights)))
+    return B200MOE_EINVAL;
+  int sms;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_gemm1_skinny(p, ws, sms, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  int rc = check_problem(p, ws);
+  if (rc) return rc;
+  if (p->T > 0 && (!p->gemm2_weights || !p->gemm2_weights_scale || !aligned16(p->gemm2_weights)))
+    return B200MOE_EINVAL;
+  int sms;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_gemm2_skinny(p, ws, sms, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_gemv1(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
@@ -314,8 +346,15 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
     if ((rc = launch_sort(p, ws, st))) return rc;
     if ((rc = launch_gather(p, ws, sms, st))) return rc;
   }
-  if ((rc = launch_gemm1(p, ws, sms, st))) return rc;
-  if ((rc = launch_gemm2(p, ws, sms, st))) return rc;
+  // Few rows per expert (8 T / 256 per expert on average): token-minor tiles, bound by streaming the weights; else
+  // 128-token tiles.  Both kernels are correct for every batch; the choice is about speed only.
+  if (p->T <= B200MOE_SKINNY_MAX_T) {
+    if ((rc = launch_gemm1_skinny(p, ws, sms, st))) return rc;
+    if ((rc = launch_gemm2_skinny(p, ws, sms, st))) return rc;
+  } else {
+    if ((rc = launch_gemm1(p, ws, sms, st))) return rc;
+    if ((rc = launch_gemm2(p, ws, sms, st))) return rc;
+  }
   return launch_reduce(p, ws, st);
 }
 

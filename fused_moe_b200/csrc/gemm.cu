@@ -37,6 +37,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace b200moe {
 
@@ -59,19 +60,6 @@ struct Cfg {
   static constexpr int STAGES = (196608 / STAGE_BYTES) > 6 ? 6 : (196608 / STAGE_BYTES);  // 4/3 (CG 1), 6/4 (CG 2)
   static constexpr int K_CHUNKS = (MODE == 1) ? H_BLOCKS : I_BLOCKS;
   static constexpr int N_TILES = (MODE == 1) ? (I / 128) : (H / 256);  // 16, 28
-};
-
-struct GemmArgs {
-  const int* block_offsets;  // [E+1]
-  const int* counts;         // [E]
-  const float* row_scale;    // MODE1: a_scale_sorted [56,R_max]; MODE2: inter_scale [16,R_max]
-  const float* w_scale;      // MODE1: [E,32,56]; MODE2: [E,56,16]
-  uint8_t* inter_q;          // MODE1 out: [2,R_max,2048]
-  float* inter_scale;        // MODE1 out: [16,R_max]
-  float* expert_out;         // MODE2 out: [R_max,7168] float32
-  int* status;
-  int E_local;
-  int R_max;
 };
 
 struct TileInfo {
@@ -119,23 +107,6 @@ struct __align__(8) GemmAux {
 template <int MODE, int CG>
 constexpr size_t gemm_smem_bytes() {
   return 1024 + static_cast<size_t>(Cfg<MODE, CG>::STAGES) * Cfg<MODE, CG>::STAGE_BYTES + sizeof(GemmAux);
-}
-
-__device__ __forceinline__ float silu_mul(float gate, float up) {
-  return __fdividef(gate, 1.0f + __expf(-gate)) * up;
-}
-
-__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
-  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
-__device__ __forceinline__ void unpack4_e4m3(uint32_t v, float (&f)[4]) {
-  __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v & 0xffffu), __NV_E4M3);
-  __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v >> 16), __NV_E4M3);
-  float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
-  float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
-  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
 template <int MODE, int CG>
@@ -522,7 +493,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D byte tensor [rows, cols] (row pitch = cols), box [box_rows, 128 bytes], 128-byte swizzle.
-static int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return record_cuda_error(cudaErrorNotSupported);
   cuuint64_t dims[2] = {cols, rows};
@@ -558,6 +529,9 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
   a.inter_scale = ws->inter_scale;
   a.expert_out = ws->expert_out;
   a.status = ws->status;
+  a.tile_ctr = nullptr;
+  a.weights = nullptr;
+  a.partial = nullptr;
   a.E_local = p->E_local;
   a.R_max = ws->R_max;
   // weight boxes: 128 rows everywhere except the single-CTA GEMM2, which takes its 256 W2 rows in one box

@@ -1,0 +1,46 @@
+// Pieces shared by the two grouped FP8 GEMM kernels (128-token tiles in gemm.cu, token-minor tiles in gemm_skinny.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp8.h>
+#include <cuda_fp16.h>
+#include "common.cuh"
+
+namespace b200moe {
+
+struct GemmArgs {
+  const int* block_offsets;  // [E+1]
+  const int* counts;         // [E]
+  const float* row_scale;    // MODE1: a_scale_sorted [56,R_max]; MODE2: inter_scale [16,R_max]
+  const float* w_scale;      // MODE1: [E,32,56]; MODE2: [E,56,16]
+  const uint8_t* weights;    // token-minor kernels: MODE1 [E,4096,7168], MODE2 [E,7168,2048] e4m3 (read without TMA)
+  uint8_t* inter_q;          // MODE1 out: [2,R_max,2048]
+  float* inter_scale;        // MODE1 out: [16,R_max]
+  float* expert_out;         // MODE2 out: [R_max,7168] float32
+  int* status;
+  int* tile_ctr;             // token-minor kernels: tickets of tiles shared by several CTAs (zero between launches)
+  float* partial;            // token-minor kernels: partial sums of shared tiles, two slots per CTA
+  int E_local;
+  int R_max;
+};
+
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ void unpack4_e4m3(uint32_t v, float (&f)[4]) {
+  __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v & 0xffffu), __NV_E4M3);
+  __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v >> 16), __NV_E4M3);
+  float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+  float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// 2-D byte tensor [rows, cols] (row pitch = cols), box [box_rows, 128 bytes], 128-byte swizzle.  Defined in gemm.cu.
+int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+}  // namespace b200moe

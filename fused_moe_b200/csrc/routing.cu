@@ -147,12 +147,14 @@ k_route(const float* __restrict__ logits, const uint16_t* __restrict__ bias, int
   if (threadIdx.x < E_local) chunk_bits[static_cast<size_t>(chunk) * E_local + threadIdx.x] = s_bits[threadIdx.x];
 }
 
-// Small batches (T <= 128): routing, ranking, padded layout, scatter and the activation gather in ONE launch instead of
+// Small batches (T <= B200MOE_PROLOGUE_MAX_T): routing, ranking, padded layout, scatter and the activation gather in ONE launch instead of
 // four.  Same results, bit for bit, as k_route + k_rank_scan + k_scatter + k_gather.  Every CTA repeats the (cheap)
 // routing and layout of the whole batch in shared memory, so no CTA waits for another; CTA 0 alone writes the metadata
 // to global memory, and the row copies are dealt round-robin over all CTAs.  1024 threads: warp w routes token 32c + w
-// of chunk c (up to four chunks, one after the other) and keeps its eight pairs in lanes 0..7 for the placement.
-constexpr int SMALL_T_MAX = 128;
+// of chunk c (chunks one after the other, which is why the limit is low: measured, one chunk costs ~9 us and the
+// separate kernels win from the second chunk on) and keeps its eight pairs in lanes 0..7 for the placement.
+constexpr int SMALL_T_MAX = B200MOE_PROLOGUE_MAX_T;
+static_assert(SMALL_T_MAX % 32 == 0 && SMALL_T_MAX <= 128, "whole token chunks, at most 1024 (token, k) pairs");
 __global__ void __launch_bounds__(1024, 1)
 k_small_prologue(const float* __restrict__ logits, const uint16_t* __restrict__ bias, const uint8_t* __restrict__ hidden,
                  const float* __restrict__ hidden_scale, int T, float scale_factor, int local_offset, int E_local,

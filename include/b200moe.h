@@ -36,7 +36,9 @@ extern "C" {
 #define B200MOE_TOPK_GROUP 4
 #define B200MOE_QBLOCK 128
 #define B200MOE_BLOCK_M 128 /* rows per expert tile; every expert segment is padded to a multiple of this */
-#define B200MOE_PROLOGUE_MAX_T 128 /* largest batch of b200moe_prologue_small */
+#define B200MOE_GEMM_MAX_CTAS 160  /* CTAs of a token-minor GEMM launch (one per SM, at most this many) */
+#define B200MOE_SKINNY_MAX_T 256   /* b200moe_forward uses the token-minor GEMM kernels up to this batch size */
+#define B200MOE_PROLOGUE_MAX_T 32  /* largest batch of b200moe_prologue_small */
 #define B200MOE_DECODE_MAX_T 2 /* up to this many tokens b200moe_forward takes the matrix-vector (decode) path */
 
 enum {
@@ -127,6 +129,9 @@ typedef struct b200moe_workspace {
   uint8_t* inter_q;          /* [2, R_max, 2048] e4m3: SwiGLU output as value term + residual term, shared scale */
   float* inter_scale;        /* [16, R_max]   per row per 128 columns */
   float* expert_out;         /* [R_max, 7168] float32 GEMM2 result per sorted row (unweighted) */
+  int32_t* gemm_tile_ctr;    /* [(R_max / 64) * 28] tickets of GEMM tiles shared by several CTAs; zero between launches
+                                (b200moe_workspace_init clears it, the kernels return it to zero) */
+  float* gemm_partial;       /* [B200MOE_GEMM_MAX_CTAS, 2, 2 * 64 * 128] float32 partial sums of shared tiles */
 } b200moe_workspace;
 
 /* Library / build identification.  No reference counterpart. */
@@ -183,6 +188,13 @@ int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* s
  * Replaces _fused_moe_gemm2_kernel (solution/python/pure_triton_impl.py:1056-1196) and the CuTe GEMM2
  * (solution/python/cute_gemm2_mma.py:250-304). */
 int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* The same two GEMMs with the operands swapped (weight rows on the M side of the MMA, at most 64 tokens on the N side):
+ * same inputs, outputs and results as b200moe_gemm1 / b200moe_gemm2, faster when experts see few tokens because a tile
+ * then costs what streaming its weights costs.  b200moe_forward picks them for T <= B200MOE_SKINNY_MAX_T.
+ * They replace the reference's small-batch GEMM buckets (_small_medium_fused_moe_gemm1_swiglu_kernel /
+ * _small_medium_fused_moe_gemm2_kernel, solution/python/pure_triton_impl.py:1278-1466). */
+int b200moe_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+int b200moe_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
 /* Decode path stages (need topk_idx / topk_w of b200moe_route in the workspace; the fp32 intermediate [T*8, 2048] is
  * kept in the workspace's expert_out array): one warp per output element streams the weight rows from HBM.
  * Replaces the reference's T = 1 path: GEMM1 with BLOCK_M = 16 (solution/python/pure_triton_impl.py:1824-1940) and

@@ -68,7 +68,7 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     assert torch.equal(idx, ref["topk_idx"]), "expert ids differ from the oracle"
     assert torch.equal(w, ref["topk_w"]), "routing weights differ from the oracle"
 
-    # sort metadata: bit-exact, as the forward call left it (for 2 < T <= 128 that is the fused single-launch prologue,
+    # sort metadata: bit-exact, as the forward call left it (for 2 < T <= 32 that is the fused single-launch prologue,
     # above it the separate sort kernels).  The decode path (T <= 2) does not sort, so the stage is run here explicitly.
     if T <= 2:
         from fused_moe_b200 import _lib
@@ -103,9 +103,11 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     (3, 2, 21, 100, False),    # no token reaches a local expert: all-zero output
     (300, 32, 4, 64, True),    # an expert with more than one 128-row block
     (12, 256, 6, 0, True),     # all 256 experts local: every token sums eight expert rows
-    (128, 32, 7, 32, False),   # largest batch of the fused prologue: four full token chunks
-    (127, 256, 8, 0, True),    # fused prologue, ragged last chunk, every pair local (1016 gathered rows)
-    (129, 32, 7, 32, False),   # first batch size on the separate route / sort / gather kernels
+    (32, 32, 7, 32, False),    # largest batch of the fused prologue: one full token chunk
+    (31, 256, 8, 0, True),     # fused prologue, ragged chunk, every pair local (248 gathered rows)
+    (33, 32, 7, 32, False),    # first batch size on the separate route / sort / gather kernels
+    (256, 32, 10, 0, True),    # largest batch on the token-minor GEMMs, experts with several 64-row sub-blocks
+    (257, 32, 10, 0, True),    # first batch size on the 128-token-tile GEMMs
 ])
 def test_layer_matches_oracle(moe, oracle, T, E_local, seed, offset, skew):
     out, ref, _ = run_and_check(moe, oracle, T, E_local, seed, offset, skew)
@@ -163,6 +165,53 @@ def test_routing_large_skewed(moe, oracle):
     _lib.check(lib.b200moe_topk_bits(C.byref(p), C.byref(ws.struct), stream), "topk_bits")
     torch.cuda.synchronize()
     assert torch.equal(ws.view("chunk_bits", torch.int32, (ws.struct.n_chunks, E_local)), bits)
+
+
+@pytest.mark.parametrize("T,E_local,seed,offset,skew", [
+    (7, 32, 3, 0, False),       # every tile shared by several CTAs (fewer tiles than SMs)
+    (150, 32, 3, 0, True),      # experts just above one 64-row sub-block
+    (300, 32, 3, 64, True),     # a left-over round with fewer chunk units than CTAs
+    (700, 32, 3, 0, True),      # experts with five sub-blocks, whole rounds plus a left-over round
+    (40, 3, 3, 253, True),      # one real row
+    (64, 256, 3, 0, False),     # all experts local
+    (2000, 8, 3, 0, True),      # above the batch size at which b200moe_forward picks these kernels
+])
+def test_token_minor_gemms_match_tile_gemms(moe, T, E_local, seed, offset, skew):
+    """b200moe_gemm1_skinny / b200moe_gemm2_skinny against b200moe_gemm1 / b200moe_gemm2 on the same sorted rows, and
+    twice in a row (the tile tickets must be back at zero after a launch).  Tiles one CTA computes alone are bit-equal;
+    tiles shared between CTAs add the same fp32 products in another association, hence the small tolerance."""
+    from fused_moe_b200 import _lib
+    from fused_moe_b200.kernel import _problem
+    lib = _lib.load()
+    inp = gpu_inputs(T, E_local, seed, offset, skew)
+    out = moe.kernel(**inp)
+    torch.cuda.synchronize()
+    ws = moe.last_workspace()
+    R = ws.struct.R_max
+    stream = torch.cuda.current_stream().cuda_stream
+    p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]), inp["routing_logits"], inp["routing_bias"],
+                 inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"],
+                 inp["gemm2_weights"], inp["gemm2_weights_scale"], out)
+    rows = int(ws.view("total_blocks", torch.int32, (1,)).item()) * 128
+    real = ws.view("sorted_token_ids", torch.int32, (R,))[:rows] < T
+
+    def run(tag):
+        ws.view("inter_q", torch.uint8, (2, R, 2048)).fill_(0x11)
+        ws.view("expert_out", torch.float32, (R, 7168)).fill_(7.0)
+        _lib.check(getattr(lib, "b200moe_gemm1" + tag)(C.byref(p), C.byref(ws.struct), stream), "gemm1" + tag)
+        _lib.check(getattr(lib, "b200moe_gemm2" + tag)(C.byref(p), C.byref(ws.struct), stream), "gemm2" + tag)
+        torch.cuda.synchronize()
+        moe.check_status()
+        return ws.view("expert_out", torch.float32, (R, 7168))[:rows][real].clone()
+
+    ref = run("")
+    first = run("_skinny")
+    second = run("_skinny")
+    assert torch.equal(first, second), "token-minor GEMMs are not repeatable"
+    assert int(ws.view("gemm_tile_ctr", torch.int32, (R // 64 * 28,)).abs().sum().item()) == 0
+    if ref.numel():
+        tol = 5e-4 * float(ref.abs().max())
+        assert float((first - ref).abs().max()) <= tol
 
 
 def test_from_topk_equals_routed(moe):
