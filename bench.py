@@ -230,6 +230,25 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
     return res, pairs, active, blocks
 
 
+def quantiser_line(K, device, peaks, T=16384, reps=20):
+    """The activation quantiser upstream of the layer (bf16 -> e4m3 + scales), timed alone: HBM-bound, 14 336 B read +
+    7 392 B written per token (352 MB at T = 16384, above L2)."""
+    x = torch.randn((T, H), dtype=torch.float32, device=device).bfloat16()
+    for _ in range(3):
+        K.quantize_activations(x)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        K.quantize_activations(x)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    gbs = T * (2 * H + H + 56 * 4) / (us * 1e-6) / 1e9
+    return dict(workload="quantize_act", T=T, us=round(us, 1), achieved_gbs=round(gbs, 1),
+                frac_of_measured_hbm=round(gbs / peaks["hbm_gbs"], 3))
+
+
 def layer_roofline(T, pairs, active, ms, peaks, tensor_peak):
     """Whole-layer bound: max(algorithmic bytes / HBM, algorithmic flops / tensor peak) over measured time."""
     bytes_alg = active * (WEIGHT_BYTES_PER_EXPERT + 7168 + 3584) + pairs * H + T * (56 * 4 + 1024 + 2 * H)
@@ -402,6 +421,7 @@ def run_ours(args):
                                   layer_bound=lr["bound"], layer_roofline_frac=round(lr["frac"], 3)))
                 del _
                 torch.cuda.empty_cache()
+            sweep.append(quantiser_line(K, device, peaks))
         if not args.no_cpu_baseline:
             cpu, _dt = cpu_baseline(lambda n: reference_inputs(args.workload, n, args.seed), args.cpu_sample_tokens,
                                     os.cpu_count() or 1)

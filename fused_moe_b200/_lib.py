@@ -99,6 +99,7 @@ SYMBOLS = {
     "b200moe_workspace_carve": (C.c_int, (C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.POINTER(Workspace))),
     "b200moe_workspace_init": (C.c_int, (C.POINTER(Workspace), C.c_void_p)),
     "b200moe_forward": (C.c_int, _PW),
+    "b200moe_quantize_act": (C.c_int, (C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p)),
     "b200moe_route": (C.c_int, _PW),
     "b200moe_topk_bits": (C.c_int, _PW),
     "b200moe_sort": (C.c_int, _PW),

@@ -21,6 +21,7 @@ int launch_sort(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
+int launch_quantize_act(const void*, int, void*, float*, int, cudaStream_t);
 int launch_gemm1_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm2_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
@@ -180,6 +181,16 @@ int b200moe_workspace_init(const b200moe_workspace* ws, void* stream) {
     B200MOE_CUDA_TRY(cudaMemsetAsync(ws->gemm_tile_ctr, 0, sizeof(int32_t) * tile_ctr_count(ws->R_max),
                                      static_cast<cudaStream_t>(stream)));
   return B200MOE_OK;
+}
+
+int b200moe_quantize_act(const void* x_bf16, int32_t T, void* q_out, float* scale_out, void* stream) {
+  if (T < 0 || T > (1 << 24)) return B200MOE_EINVAL;
+  if (T > 0 && (!x_bf16 || !q_out || !scale_out)) return B200MOE_EINVAL;
+  if (T > 0 && ((reinterpret_cast<uintptr_t>(x_bf16) & 7u) || (reinterpret_cast<uintptr_t>(q_out) & 3u)))
+    return B200MOE_EINVAL;
+  int sms, rc;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_quantize_act(x_bf16, T, q_out, scale_out, sms, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_route(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {

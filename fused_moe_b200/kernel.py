@@ -215,6 +215,27 @@ def kernel(
 
 
 @torch.no_grad()
+def quantize_activations(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 activations [T, 7168] -> (e4m3 [T, 7168], float32 scales [56, T]): the ``hidden_states`` /
+    ``hidden_states_scale`` pair ``kernel`` takes, one scale per token per 128 columns (``b200moe_quantize_act``).
+    The reference has no operator for this step; its profiling script builds the pair with torch
+    (scripts/yjl_ncu.py:413-416)."""
+    _require(x, "x", torch.bfloat16, (x.shape[0] if torch.is_tensor(x) and x.dim() == 2 else -1, H))
+    _require_cuda(x=x)
+    x = x.contiguous()
+    T = x.shape[0]
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((H // 128, T), dtype=torch.float32, device=x.device)
+    if T == 0:
+        return q, s
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().b200moe_quantize_act(x.data_ptr(), T, q.data_ptr(), s.data_ptr(),
+                                                    torch.cuda.current_stream(x.device).cuda_stream),
+                   "b200moe_quantize_act")
+    return q, s
+
+
+@torch.no_grad()
 def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
                      gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None,
                      out_dtype=torch.bfloat16):

@@ -91,13 +91,20 @@ def quantize_weight(w: torch.Tensor):
 
 def make_inputs(T: int, E_local: int = 32, seed: int = 0, local_expert_offset: int = 0, skew: bool = False,
                 device="cpu", routed_scaling_factor: float = 2.5, weights: Optional[Dict] = None,
-                only_experts=None) -> Dict:
+                only_experts=None, heavy_tail: bool = False) -> Dict:
     """Keyword arguments for ``kernel(**inputs)``.  ``weights`` (a previous result) lets callers reuse the expert
     weights, which dominate generation time; expert e of the result is GLOBAL expert local_expert_offset+e, so
     shards of an expert-parallel run see consistent weights.  ``only_experts`` (local ids) generates just those
-    experts and leaves the others zero — CPU tests use it to skip experts no token reaches."""
+    experts and leaves the others zero — CPU tests use it to skip experts no token reaches.  ``heavy_tail`` gives the
+    activations a log-normal magnitude per token (x 0.01 .. x 100) and 20x outliers on ~0.3 % of the elements, so the
+    SwiGLU intermediates span the range reported for real traces (p99 above 1e4) instead of staying near 1."""
     dev = torch.device(device)
-    hs = normal(T * H, seed, 1, device=dev).view(T, H).bfloat16().float()
+    hs = normal(T * H, seed, 1, device=dev).view(T, H)
+    if heavy_tail:
+        mag = torch.exp(2.3 * normal(T, seed, 7, device=dev).clamp(-2.0, 2.0)).view(T, 1)
+        spike = normal(T * H, seed, 8, device=dev).view(T, H).abs() > 3.0
+        hs = hs * mag * torch.where(spike, 20.0, 1.0)
+    hs = hs.bfloat16().float()
     hs_q, hs_s = quantize_act(hs)
     logits = normal(T * E_GLOBAL, seed, 2, device=dev).view(T, E_GLOBAL)
     if skew:

@@ -21,8 +21,10 @@ def pytest_configure(config):
 
 def load_golden(name):
     d = np.load(GOLDEN_DIR / f"{name}.npz")
-    T, E_local, offset, seed, skew, full = (int(x) for x in d["meta"])
-    rec = dict(T=T, E_local=E_local, offset=offset, seed=seed, skew=bool(skew), full=bool(full),
+    meta = [int(x) for x in d["meta"]]
+    T, E_local, offset, seed, skew, full = meta[:6]
+    heavy = bool(meta[6]) if len(meta) > 6 else False   # heavy-tailed activations (synth.make_inputs(heavy_tail=True))
+    rec = dict(T=T, E_local=E_local, offset=offset, seed=seed, skew=bool(skew), full=bool(full), heavy=heavy,
                topk_idx=d["topk_idx"].astype(np.int64), topk_w=d["topk_w"])
     if full:
         rec["out_f32"] = d["out_f32"]
@@ -60,3 +62,28 @@ def oracle():
     import oracle as oracle_mod
     oracle_mod.build()
     return oracle_mod
+
+
+def assert_close_rowscaled(actual, expected, rel, what="output"):
+    """|x - y| <= rel * max(1, max_j |y[row, j]|): the error bound of sums whose terms are as large as the row's largest
+    value, used where rows span many orders of magnitude (heavy-tailed activations).  Returns the worst error as a
+    fraction of that bound."""
+    import torch
+    a = torch.as_tensor(actual).float()
+    e = torch.as_tensor(expected).float()
+    assert a.shape == e.shape and torch.isfinite(a).all(), f"{what}: shape or non-finite values"
+    bound = rel * e.abs().amax(dim=1, keepdim=True).clamp_min(1.0)
+    worst = ((a - e).abs() / bound).max().item()
+    assert worst <= 1.0, f"{what}: max error is {worst:.3f} x the row-scaled bound (rel = {rel})"
+    return worst
+
+
+def matched_ratio(actual, expected, atol=1.0, rtol=0.3):
+    """The contest harness's criterion (the reference's test_bench.py:224-231 runs it with atol 1, rtol 0.3 and requires
+    a ratio >= 0.9): an element fails only if its absolute error exceeds atol AND its relative error exceeds rtol."""
+    import torch
+    a = torch.as_tensor(actual).float()
+    e = torch.as_tensor(expected).float()
+    err = (a - e).abs()
+    fail = (err > atol) & (err > rtol * e.abs())
+    return 1.0 - fail.float().mean().item()

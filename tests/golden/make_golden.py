@@ -27,13 +27,15 @@ from fused_moe_b200 import synth  # noqa: E402
 
 REFERENCE_DIR = Path(os.environ.get("REFERENCE_DIR", "/root/reference"))
 
-# name -> dict(T, E_local, offset, seed, skew, full)   full=False: routing only (no expert weights needed)
+# name -> dict(T, E_local, offset, seed, skew, full[, heavy])   full=False: routing only (no expert weights needed);
+# heavy=True: heavy-tailed activations (synth.make_inputs(heavy_tail=True))
 CASES = {
     "config0_t7_e32": dict(T=7, E_local=32, offset=0, seed=0, skew=False, full=True),
     "t1_e32": dict(T=1, E_local=32, offset=96, seed=5, skew=False, full=True),
     "t33_e8_off60": dict(T=33, E_local=8, offset=60, seed=3, skew=False, full=True),
     "t40_e3_off253_skew": dict(T=40, E_local=3, offset=253, seed=13, skew=True, full=True),
     "t3_e2_none_local": dict(T=3, E_local=2, offset=100, seed=21, skew=False, full=True),
+    "t12_e8_off16_heavy_tail": dict(T=12, E_local=8, offset=16, seed=34, skew=False, full=True, heavy=True),
     "route_t4096_skew": dict(T=4096, E_local=32, offset=0, seed=7, skew=True, full=False),
     "route_t1000": dict(T=1000, E_local=32, offset=0, seed=8, skew=False, full=False),
 }
@@ -56,18 +58,22 @@ def sorted_routing(idx: torch.Tensor, w: torch.Tensor):
 def main():
     torch.set_num_threads(os.cpu_count() or 1)
     bind = load_binding()
+    only = set(sys.argv[1:])   # optional: regenerate just the named cases
     for name, c in CASES.items():
+        if only and name not in only:
+            continue
         base = synth.make_inputs(c["T"], c["E_local"], seed=c["seed"], local_expert_offset=c["offset"],
-                                 skew=c["skew"], only_experts=[])
+                                 skew=c["skew"], only_experts=[], heavy_tail=c.get("heavy", False))
         idx, w = bind._ds_routing_impl(base["routing_logits"], base["routing_bias"], base["routed_scaling_factor"])
         sidx, sw = sorted_routing(idx, w)
         rec = dict(topk_idx=sidx.numpy().astype(np.int16), topk_w=sw.numpy().astype(np.float32),
-                   meta=np.array([c["T"], c["E_local"], c["offset"], c["seed"], int(c["skew"]), int(c["full"])]))
+                   meta=np.array([c["T"], c["E_local"], c["offset"], c["seed"], int(c["skew"]), int(c["full"]),
+                                  int(c.get("heavy", False))]))
         if c["full"]:
             local = idx - c["offset"]
             hit = sorted(set(local[(local >= 0) & (local < c["E_local"])].tolist()))
             inp = synth.make_inputs(c["T"], c["E_local"], seed=c["seed"], local_expert_offset=c["offset"],
-                                    skew=c["skew"], only_experts=hit)
+                                    skew=c["skew"], only_experts=hit, heavy_tail=c.get("heavy", False))
             bind.E_LOCAL = c["E_local"]
             bind._buf_cache.clear()
             out = torch.zeros((c["T"], 7168), dtype=torch.float32)

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close, golden_names, load_golden
+from conftest import assert_close, assert_close_rowscaled, golden_names, load_golden, matched_ratio
 
 pytestmark = pytest.mark.gpu
 
@@ -30,13 +30,14 @@ def moe():
 _weights_cache = {}
 
 
-def gpu_inputs(T, E_local, seed, offset, skew):
+def gpu_inputs(T, E_local, seed, offset, skew, heavy=False):
     from fused_moe_b200 import synth
     key = (E_local, seed, offset)
     w = _weights_cache.get(key)
     if w is None:
         _weights_cache.clear()
-    inp = synth.make_inputs(T, E_local, seed=seed, local_expert_offset=offset, skew=skew, device="cuda", weights=w)
+    inp = synth.make_inputs(T, E_local, seed=seed, local_expert_offset=offset, skew=skew, device="cuda", weights=w,
+                            heavy_tail=heavy)
     _weights_cache[key] = inp
     return inp
 
@@ -119,13 +120,21 @@ def test_layer_matches_oracle(moe, oracle, T, E_local, seed, offset, skew):
 def test_layer_matches_reference_golden(moe, name):
     """Straight against the reference's own outputs (tests/golden, made by solution/cuda/binding.py)."""
     g = load_golden(name)
-    inp = gpu_inputs(g["T"], g["E_local"], g["seed"], g["offset"], g["skew"])
+    inp = gpu_inputs(g["T"], g["E_local"], g["seed"], g["offset"], g["skew"], g["heavy"])
     out = moe.kernel(**inp)
     moe.check_status()
     ws = moe.last_workspace()
     idx = ws.view("topk_idx", torch.int32, (g["T"], 8)).cpu().long()
     assert np.array_equal(idx.sort(dim=1).values.numpy(), g["topk_idx"])
-    assert_close(out.float().cpu(), torch.from_numpy(g["out_f32"]).bfloat16().float(), what=name)
+    ref = torch.from_numpy(g["out_f32"]).bfloat16().float()
+    if g["heavy"]:
+        # Heavy-tailed activations (rows from 1e-2 to 3e4, elements that cancel to ~0): an element-wise 1e-2 + 2e-2 |y|
+        # cannot hold for any FP8 product there.  Checked instead: the contest's own criterion for real traces, and an
+        # error bound relative to each row's largest value, which is what the two-term FP8 intermediate must deliver.
+        assert matched_ratio(out.float().cpu(), ref) >= 0.999
+        assert_close_rowscaled(out.float().cpu(), ref, rel=1e-2, what=name)
+        return
+    assert_close(out.float().cpu(), ref, what=name)
 
 
 def test_routing_large_skewed(moe, oracle):
@@ -304,3 +313,24 @@ def test_synth_cpu_and_cuda_generate_identical_bytes(moe):
             y = b[k].cpu()
             y = y.view(torch.uint8) if y.dtype == torch.float8_e4m3fn else y
             assert torch.equal(x, y), k
+
+
+@pytest.mark.parametrize("T,heavy", [(1, False), (33, True), (1000, False)])
+def test_quantize_activations_matches_generator(moe, T, heavy):
+    """b200moe_quantize_act against the torch arithmetic of the input generator (synth.quantize_act): identical bytes and
+    scales, including an all-zero row (scale clamps to 1e-12, codes 0) and heavy-tailed rows."""
+    from fused_moe_b200 import synth
+    x = synth.normal(T * 7168, 77, 1, device="cuda").view(T, 7168)
+    if heavy:
+        x = x * torch.exp(2.3 * synth.normal(T, 77, 7, device="cuda").clamp(-2, 2)).view(T, 1)
+        x[T // 2].zero_()
+    xb = x.bfloat16()
+    q_ref, s_ref = synth.quantize_act(xb.float())
+    q, s = moe.quantize_activations(xb)
+    torch.cuda.synchronize()
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    with pytest.raises(TypeError):
+        moe.quantize_activations(x)           # float32 input
+    with pytest.raises(ValueError):
+        moe.quantize_activations(xb[:, :128])  # wrong width
