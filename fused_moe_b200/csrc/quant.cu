@@ -17,27 +17,39 @@ k_quantize_act(const uint2* __restrict__ x, int T, uint32_t* __restrict__ q, flo
   const long long total = static_cast<long long>(T) * H_BLOCKS;
   pdl_launch_dependents();
   pdl_wait();
-  for (long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p < total; p += warps) {
-    const uint2 raw = __ldg(x + p * 32 + lane);   // 4 bf16
-    float v[4];
-    v[0] = __uint_as_float(raw.x << 16);
-    v[1] = __uint_as_float(raw.x & 0xffff0000u);
-    v[2] = __uint_as_float(raw.y << 16);
-    v[3] = __uint_as_float(raw.y & 0xffff0000u);
-    // |x| of non-negative floats orders like their bit patterns
-    const uint32_t m4 = max(max(__float_as_uint(fabsf(v[0])), __float_as_uint(fabsf(v[1]))),
-                            max(__float_as_uint(fabsf(v[2])), __float_as_uint(fabsf(v[3]))));
-    const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, m4));
-    const float s = fmaxf(__fmul_rn(amax, 1.0f / 448.0f), 1e-12f);
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[0], s), __fdiv_rn(v[1], s)), __NV_SATFINITE,
-                                                 __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2], s), __fdiv_rn(v[3], s)), __NV_SATFINITE,
-                                                 __NV_E4M3);
-    q[p * 32 + lane] = lo | (hi << 16);
-    if (lane == 0) {
-      const long long t = p / H_BLOCKS;
-      const int kb = static_cast<int>(p - t * H_BLOCKS);
-      scale[static_cast<size_t>(kb) * T + t] = s;
+  constexpr int UNROLL = 4;   // independent blocks per warp and iteration: 4 x 256 B in flight per warp
+  for (long long p0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p0 < total;
+       p0 += warps * UNROLL) {
+    uint2 raw[UNROLL];
+#pragma unroll
+    for (int i = 0; i < UNROLL; ++i) {
+      const long long p = p0 + i * warps;
+      raw[i] = p < total ? __ldg(x + p * 32 + lane) : make_uint2(0u, 0u);   // 4 bf16
+    }
+#pragma unroll
+    for (int i = 0; i < UNROLL; ++i) {
+      const long long p = p0 + i * warps;
+      if (p >= total) break;
+      float v[4];
+      v[0] = __uint_as_float(raw[i].x << 16);
+      v[1] = __uint_as_float(raw[i].x & 0xffff0000u);
+      v[2] = __uint_as_float(raw[i].y << 16);
+      v[3] = __uint_as_float(raw[i].y & 0xffff0000u);
+      // |x| of non-negative floats orders like their bit patterns
+      const uint32_t m4 = max(max(__float_as_uint(fabsf(v[0])), __float_as_uint(fabsf(v[1]))),
+                              max(__float_as_uint(fabsf(v[2])), __float_as_uint(fabsf(v[3]))));
+      const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, m4));
+      const float s = fmaxf(__fmul_rn(amax, 1.0f / 448.0f), 1e-12f);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[0], s), __fdiv_rn(v[1], s)),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2], s), __fdiv_rn(v[3], s)),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      q[p * 32 + lane] = lo | (hi << 16);
+      if (lane == 0) {
+        const long long t = p / H_BLOCKS;
+        const int kb = static_cast<int>(p - t * H_BLOCKS);
+        scale[static_cast<size_t>(kb) * T + t] = s;
+      }
     }
   }
 }
@@ -45,7 +57,7 @@ k_quantize_act(const uint2* __restrict__ x, int T, uint32_t* __restrict__ q, flo
 int launch_quantize_act(const void* x, int T, void* q, float* scale, int num_sms, cudaStream_t st) {
   if (T == 0) return B200MOE_OK;
   const long long total = static_cast<long long>(T) * H_BLOCKS;
-  long long ctas = (total + 7) / 8;
+  long long ctas = (total + 31) / 32;   // 8 warps x 4 blocks per CTA and iteration
   const long long cap = static_cast<long long>(num_sms) * 8;   // 8 resident CTAs of 256 threads per SM
   if (ctas > cap) ctas = cap;
   B200MOE_CUDA_TRY(launch_pdl(k_quantize_act, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, st,
