@@ -198,6 +198,11 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 }
 __device__ __forceinline__ void setmaxnreg_inc_promo() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 __device__ __forceinline__ void setmaxnreg_dec_aux() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+// Same pool split differently (one warpgroup at DEC, two at INC; 128 * DEC + 256 * INC <= 64512 registers).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 
 // ---------------------------------------------------------------------------------------------------------

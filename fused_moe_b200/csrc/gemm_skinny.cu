@@ -31,7 +31,7 @@
 // over the weights.  -DSKINNY_W_VIA_TMA=1 builds the TMA variant.
 //
 // Roles, pipeline, bounded waits and teardown are those of gemm.cu: 8 promotion warps (warp w: TMEM lanes 32*(w%4)..,
-// token columns of half w/4), one TMA thread, one MMA thread, two TMEM stages, `setmaxnreg` 232 / 40.
+// token columns of half w/4), one TMA thread, one MMA thread, two TMEM stages, `setmaxnreg` 224 / 56.
 // A tile that one CTA computes alone gives bit for bit what gemm.cu gives (same products, same order); a shared tile
 // adds the same products in a different association (last-bit differences in fp32).
 #include <cuda.h>
@@ -417,7 +417,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   };
 
   if (warp >= NUM_PROMO_WARPS) {
-    setmaxnreg_dec_aux();
+    setmaxnreg_dec<56>();   // the loader warps keep 32 row addresses in flight
     if (warp == PRODUCER_WARP) {
       // ------------------------------------------------------------------ TMA producer (one thread)
       if (lane == 0) {
@@ -575,7 +575,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     }
 #endif
   } else {
-    setmaxnreg_inc_promo();
+    setmaxnreg_inc<224>();
     // ------------------------------------------------------------------ promotion + epilogue (8 warps)
     PromoState ps;
     bool ok = true;

@@ -1,6 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own PyTorch path on seeded inputs.
 
-Run in a container that has the reference checkout (default /root/reference; override with REFERENCE_DIR):
+Run where the reference checkout is available (default: a directory `reference` next to this repository; override
+with REFERENCE_DIR):
 
     python tests/golden/make_golden.py
 
@@ -25,7 +26,7 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
 from fused_moe_b200 import synth  # noqa: E402
 
-REFERENCE_DIR = Path(os.environ.get("REFERENCE_DIR", "/root/reference"))
+REFERENCE_DIR = Path(os.environ.get("REFERENCE_DIR", str(HERE.parent.parent.parent / "reference")))
 
 # name -> dict(T, E_local, offset, seed, skew, full[, heavy])   full=False: routing only (no expert weights needed);
 # heavy=True: heavy-tailed activations (synth.make_inputs(heavy_tail=True))
