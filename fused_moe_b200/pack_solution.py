@@ -6,7 +6,7 @@ hardware, entry point ``kernel.py::kernel``, destination-passing style) and ``so
 text files that the harness writes to a directory and imports.  This module emits the same document for this
 repository's code:
 
-* ``kernel.py`` at the top level is a shim: it builds ``libb200moe.so`` with nvcc on first import (the JSON format
+* ``kernel.py`` at the top level is a shim (imported by the harness as a submodule of a generated package): it builds ``libb200moe.so`` with nvcc on first import (the JSON format
   carries text only, so the library cannot travel prebuilt) and re-exports ``fused_moe_b200.kernel.kernel``;
 * the package (``fused_moe_b200/*.py``, ``fused_moe_b200/csrc/*``) and ``include/b200moe.h`` keep their relative paths,
   which is what ``fused_moe_b200/build.py`` expects.
@@ -23,11 +23,13 @@ from typing import Dict, List
 ROOT = Path(__file__).resolve().parent.parent
 DEFINITION = "moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048"
 
+# The harness writes the sources under <cache>/<pkg>/ and imports <pkg>.kernel (flashinfer_bench
+# compile/builders/python_builder.py), so the shim reaches the package with relative imports.
 SHIM = '''"""Entry point for the benchmark harness: builds the CUDA library once, then forwards to the package."""
-import fused_moe_b200.build as _build
+from .fused_moe_b200 import build as _build
 
 _build.build()          # nvcc, sm_100a; raises if the toolkit is missing: there is no fallback
-from fused_moe_b200.kernel import kernel  # noqa: E402,F401
+from .fused_moe_b200.kernel import kernel  # noqa: E402,F401
 '''
 
 # what the operator needs at run time; tests, oracle, bench and the expert-parallel plumbing stay out
