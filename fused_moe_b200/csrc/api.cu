@@ -186,7 +186,7 @@ int b200moe_workspace_init(const b200moe_workspace* ws, void* stream) {
 int b200moe_quantize_act(const void* x_bf16, int32_t T, void* q_out, float* scale_out, void* stream) {
   if (T < 0 || T > (1 << 24)) return B200MOE_EINVAL;
   if (T > 0 && (!x_bf16 || !q_out || !scale_out)) return B200MOE_EINVAL;
-  if (T > 0 && ((reinterpret_cast<uintptr_t>(x_bf16) & 7u) || (reinterpret_cast<uintptr_t>(q_out) & 3u)))
+  if (T > 0 && ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) || (reinterpret_cast<uintptr_t>(q_out) & 7u)))
     return B200MOE_EINVAL;
   int sms, rc;
   if ((rc = device_info(&sms))) return rc;

@@ -4,8 +4,8 @@
 // script builds them with torch: scripts/yjl_ncu.py:413-416).  Same arithmetic as the synthetic-input generator
 // (fused_moe_b200/synth.py: quantize_act), operation for operation, so the bytes are identical:
 //   s = max(amax * (1/448), 1e-12)      q = e4m3_rn(x / s)        (the code of the IEEE quotient, see quantize_pair)
-// HBM-bound: 14 336 B read + 7 392 B written per token.  One warp per (token, 128-column block): lane l holds columns
-// 4l..4l+3 (one 8-byte load, one 4-byte store, both fully coalesced over the warp), the maximum is one `redux.sync`.
+// HBM-bound: 14 336 B read + 7 392 B written per token.  One half-warp per (token, 128-column block): a lane holds 8
+// columns (one 16-byte load, one 8-byte store, both fully coalesced), the maximum is one `redux.sync` over 16 lanes.
 #include "common.cuh"
 
 namespace b200moe {
@@ -25,40 +25,45 @@ __device__ __forceinline__ uint32_t quantize_pair(float a, float b, float s, flo
 }
 
 __global__ void __launch_bounds__(256)
-k_quantize_act(const uint2* __restrict__ x, int T, uint32_t* __restrict__ q, float* __restrict__ scale) {
+k_quantize_act(const uint4* __restrict__ x, int T, uint2* __restrict__ q, float* __restrict__ scale) {
   const int lane = threadIdx.x & 31;
-  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  const long long total = static_cast<long long>(T) * H_BLOCKS;
+  const int sub = lane & 15;        // lane within the half-warp that owns one 128-column block
+  const uint32_t half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+  const long long half_warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 4);
+  const long long total = static_cast<long long>(T) * H_BLOCKS;   // 128-column blocks
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int UNROLL = 4;   // independent blocks per warp and iteration: 4 x 256 B in flight per warp
-  for (long long p0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p0 < total;
-       p0 += warps * UNROLL) {
-    uint2 raw[UNROLL];
+  constexpr int UNROLL = 2;   // independent blocks per half-warp and iteration
+  for (long long p0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4); p0 < total;
+       p0 += half_warps * UNROLL) {
+    uint4 raw[UNROLL];
 #pragma unroll
     for (int i = 0; i < UNROLL; ++i) {
-      const long long p = p0 + i * warps;
-      raw[i] = p < total ? __ldg(x + p * 32 + lane) : make_uint2(0u, 0u);   // 4 bf16
+      const long long p = p0 + i * half_warps;
+      raw[i] = p < total ? __ldg(x + p * 16 + sub) : make_uint4(0u, 0u, 0u, 0u);   // 8 bf16
     }
 #pragma unroll
     for (int i = 0; i < UNROLL; ++i) {
-      const long long p = p0 + i * warps;
-      if (p >= total) break;
-      float v[4];
-      v[0] = __uint_as_float(raw[i].x << 16);
-      v[1] = __uint_as_float(raw[i].x & 0xffff0000u);
-      v[2] = __uint_as_float(raw[i].y << 16);
-      v[3] = __uint_as_float(raw[i].y & 0xffff0000u);
-      // |x| of non-negative floats orders like their bit patterns
-      const uint32_t m4 = max(max(__float_as_uint(fabsf(v[0])), __float_as_uint(fabsf(v[1]))),
-                              max(__float_as_uint(fabsf(v[2])), __float_as_uint(fabsf(v[3]))));
-      const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, m4));
+      const long long p = p0 + i * half_warps;
+      if (p >= total) break;   // uniform over the half-warp
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+      float v[8];
+      uint32_t m = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        // |x| of non-negative floats orders like their bit patterns
+        m = max(m, max((w[j] << 16) & 0x7fffffffu, w[j] & 0x7fff0000u));
+      }
+      const float amax = __uint_as_float(__reduce_max_sync(half_mask, m));
       const float s = fmaxf(__fmul_rn(amax, 1.0f / 448.0f), 1e-12f);
       const float r = __frcp_rn(s);
-      const uint32_t lo = quantize_pair(v[0], v[1], s, r);
-      const uint32_t hi = quantize_pair(v[2], v[3], s, r);
-      q[p * 32 + lane] = lo | (hi << 16);
-      if (lane == 0) {
+      uint2 out;
+      out.x = quantize_pair(v[0], v[1], s, r) | (quantize_pair(v[2], v[3], s, r) << 16);
+      out.y = quantize_pair(v[4], v[5], s, r) | (quantize_pair(v[6], v[7], s, r) << 16);
+      q[p * 16 + sub] = out;
+      if (sub == 0) {
         const long long t = p / H_BLOCKS;
         const int kb = static_cast<int>(p - t * H_BLOCKS);
         scale[static_cast<size_t>(kb) * T + t] = s;
@@ -70,11 +75,11 @@ k_quantize_act(const uint2* __restrict__ x, int T, uint32_t* __restrict__ q, flo
 int launch_quantize_act(const void* x, int T, void* q, float* scale, int num_sms, cudaStream_t st) {
   if (T == 0) return B200MOE_OK;
   const long long total = static_cast<long long>(T) * H_BLOCKS;
-  long long ctas = (total + 31) / 32;   // 8 warps x 4 blocks per CTA and iteration
+  long long ctas = (total + 31) / 32;   // 16 half-warps x 2 blocks per CTA and iteration
   const long long cap = static_cast<long long>(num_sms) * 8;   // 8 resident CTAs of 256 threads per SM
   if (ctas > cap) ctas = cap;
   B200MOE_CUDA_TRY(launch_pdl(k_quantize_act, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, st,
-                              static_cast<const uint2*>(x), T, static_cast<uint32_t*>(q), scale));
+                              static_cast<const uint4*>(x), T, static_cast<uint2*>(q), scale));
   return B200MOE_OK;
 }
 
