@@ -130,25 +130,6 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t b) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
-// The deal.  Whole rounds first: tile r G + c goes to CTA c as one piece (r < rounds).  The tiles that are left (fewer
-// than G, numbered from first_tile) are dealt in 128-K chunk units: CTA c owns units [begin(c), begin(c + 1)) of the
-// U = left-over tiles x chunks per tile, so the last round keeps every SM busy for the same time.  With fewer units
-// than CTAs only the first U CTAs take part, so the owners of a tile's units are always consecutive CTAs.
-struct Deal {
-  long long U;      // chunk units of the left-over tiles
-  int G;            // CTAs
-  int rounds;       // whole tiles per CTA
-  int first_tile;   // = rounds * G
-  int Gu;           // CTAs that take part in the unit deal = min(G, U): every one of them owns at least one unit
-  __device__ __forceinline__ long long begin(int c) const { return c >= Gu ? U : U * c / Gu; }
-  // the CTA that owns unit u: the largest c < Gu with begin(c) <= u
-  __device__ __forceinline__ int owner(long long u) const { return static_cast<int>(((u + 1) * Gu + U - 1) / U) - 1; }
-};
-
-struct Item {
-  int tile, kb0, kb1;   // chunks [kb0, kb1) of the tile
-};
-
 // Per-thread state of a promotion warp that lives across work items.
 struct PromoState {
   int acc = 0;
@@ -389,31 +370,13 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const uint32_t tmem_base = aux->tmem_base;
   const int total_tiles = aux->grp[E] * NT;
   volatile int* abort_flag = &aux->abort_flag;
-  Deal deal;
-  deal.G = static_cast<int>(gridDim.x);
-  deal.rounds = total_tiles / deal.G;
-  deal.first_tile = deal.rounds * deal.G;
-  deal.U = static_cast<long long>(total_tiles - deal.first_tile) * C::K_CHUNKS;
-  deal.Gu = deal.U < deal.G ? static_cast<int>(deal.U) : deal.G;
+  const Deal deal = make_deal(total_tiles, C::K_CHUNKS, static_cast<int>(gridDim.x));
   const long long u_begin = deal.begin(blockIdx.x), u_end = deal.begin(blockIdx.x + 1);
   // This CTA's work as one sequence of chunk positions: its whole tiles, then its run of left-over units.
   const long long v_whole = static_cast<long long>(deal.rounds) * C::K_CHUNKS;
   const long long v_end = v_whole + (u_end - u_begin);
   auto item_at = [&](long long v) {
-    Item it;
-    if (v < v_whole) {
-      it.tile = static_cast<int>(v / C::K_CHUNKS) * deal.G + static_cast<int>(blockIdx.x);
-      it.kb0 = 0;
-      it.kb1 = C::K_CHUNKS;
-    } else {
-      const long long u = u_begin + (v - v_whole);
-      const int lt = static_cast<int>(u / C::K_CHUNKS);
-      it.tile = deal.first_tile + lt;
-      it.kb0 = static_cast<int>(u - static_cast<long long>(lt) * C::K_CHUNKS);
-      const long long left = u_end - u;
-      it.kb1 = (left < C::K_CHUNKS - it.kb0) ? it.kb0 + static_cast<int>(left) : C::K_CHUNKS;
-    }
-    return it;
+    return deal_item(deal, C::K_CHUNKS, static_cast<int>(blockIdx.x), v, v_whole, u_begin, u_end);
   };
 
   if (warp >= NUM_PROMO_WARPS) {
