@@ -8,7 +8,8 @@ GPUs (256/N local experts per GPU, tokens split evenly, expert-parallel dispatch
 to the N = 1 line under "sweep".
 
 Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events, inputs resident in HBM, max over ranks);
-`e2e` is the same metric through the public `kernel()` call with the per-step tensors starting in pinned host memory
+`e2e` is the same metric through the public host-memory call (`kernel_host()`; under expert parallelism copies around
+`shard.forward()`) with the per-step tensors starting in pinned host memory
 and the result copied back (expert weights are layer parameters and stay resident).  `roofline` describes the dominant
 kernel (GEMM1+SwiGLU) from its own CUDA-event timing; `cpu_baseline` times the CPU restatement of the reference's
 fp32-dequant path (oracle/) on a bounded sample.  `--impl reference` runs only that CPU path.
@@ -69,49 +70,86 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock and clock-event (throttle) reasons of one GPU every 5 ms while the timed region runs: NVML in a
+    thread of this process (reading only); `nvidia-smi -lms` as the fallback when the NVML module is missing."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    SMI_FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NVML_REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+                    (0x4, "sw_power_cap"))
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.stop = threading.Event()
+        self.nvml = self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+
+    def _sample_nvml(self):
+        nv = self.nvml
+        mhz = int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+        try:
+            mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+        except Exception:
+            mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+        self.rows.append((mhz, self.max_mhz, [name for bit, name in self.NVML_REASONS if mask & bit]))
+
+    def _poll_nvml(self):
+        while not self.stop.is_set():
+            try:
+                self._sample_nvml()
+            except Exception:
+                return
+            self.stop.wait(0.005)
+
+    def _read_smi(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.proc.stdout:
+            r = [x.strip() for x in line.split(",")]
+            try:
+                self.rows.append((int(float(r[0])), int(float(r[1])),
+                                  [n for n, v in zip(names, r[2:6]) if v.lower().startswith("active")]))
+            except (ValueError, IndexError):
+                continue
 
     def __enter__(self):
+        if self.nvml is not None:
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.SMI_FIELDS}", "--format=csv,noheader,nounits",
                  "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
-
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
-        mhz, mx, reasons = [], 0, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                mhz.append(int(float(r[0])))
-                mx = max(mx, int(float(r[1])))
-            except (ValueError, IndexError):
-                continue
-            for n, v in zip(names, r[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        mhz.sort()
-        return dict(sm_mhz=(mhz[len(mhz) // 2] if mhz else None), sm_max_mhz=mx or None, reasons=sorted(reasons),
+        mhz = sorted(r[0] for r in self.rows)
+        mx = max((r[1] for r in self.rows), default=0)
+        reasons = sorted({n for r in self.rows for n in r[2]})
+        return dict(sm_mhz=(mhz[len(mhz) // 2] if mhz else None), sm_max_mhz=mx or None, reasons=reasons,
                     samples=len(mhz))
 
 
@@ -331,13 +369,14 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     d2h = out_host.numel() * 2
 
     def e2e_step():
-        dev_in = {k: v.to(device, non_blocking=True) for k, v in host.items()}
         if world == 1:
-            o = K.kernel(dev_in["routing_logits"], inp["routing_bias"], dev_in["hidden_states"],
-                         dev_in["hidden_states_scale"], *pos[4:], out)
-        else:
-            o = shard.forward(dev_in["routing_logits"], inp["routing_bias"], dev_in["hidden_states"],
-                              dev_in["hidden_states_scale"], inp["routed_scaling_factor"], out)
+            # the host-memory entry point: copies in, layer and copies out pipelined over token slices
+            K.kernel_host(host["routing_logits"], inp["routing_bias"], host["hidden_states"],
+                          host["hidden_states_scale"], *pos[4:], out_host)
+            return
+        dev_in = {k: v.to(device, non_blocking=True) for k, v in host.items()}
+        o = shard.forward(dev_in["routing_logits"], inp["routing_bias"], dev_in["hidden_states"],
+                          dev_in["hidden_states_scale"], inp["routed_scaling_factor"], out)
         out_host.copy_(o, non_blocking=True)
     e2e_ms = timed_loop(e2e_step, steps, 3, world, device)
     rec["e2e"] = dict(value=T_global / (e2e_ms * 1e-3), unit="tokens/s", ms_per_step=e2e_ms,

@@ -214,6 +214,109 @@ def kernel(
     return _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, None, None)
 
 
+_host_pipes: Dict[int, dict] = {}
+
+
+def _host_pipe(device: torch.device, T: int, t_slice: int) -> dict:
+    """Copy streams, events and the two sets of staging buffers of ``kernel_host`` (one per device, resized on demand)."""
+    st = _host_pipes.get(device.index)
+    if st is None or st["t_slice"] < t_slice or st["T"] < T:
+        st = dict(t_slice=t_slice, T=T, h2d=torch.cuda.Stream(device), d2h=torch.cuda.Stream(device),
+                  logits=[torch.empty((t_slice, E_GLOBAL), dtype=torch.float32, device=device) for _ in range(2)],
+                  hs=[torch.empty((t_slice, H), dtype=_FP8, device=device) for _ in range(2)],
+                  out=[torch.empty((t_slice, H), dtype=torch.bfloat16, device=device) for _ in range(2)],
+                  scale=torch.empty((H_BLOCKS, T), dtype=torch.float32, device=device))
+        _host_pipes[device.index] = st
+    return st
+
+
+@torch.no_grad()
+def kernel_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output=None,
+                slices: Optional[int] = None):
+    """``kernel`` for activations that live in HOST memory: ``routing_logits``, ``hidden_states``,
+    ``hidden_states_scale`` and ``output`` are pinned host tensors (``output=None`` allocates one), the bias and the
+    expert weights are device tensors as in ``kernel``.  The tokens are cut into ``slices`` equal runs (default: chosen
+    from the batch size and the number of local experts, see below) and pipelined over three streams, so the host-to-device copy of run i + 1 and the
+    device-to-host copy of run i - 1 overlap the layer on run i; rows are independent, so the result equals one
+    ``kernel`` call on all tokens bit for bit.  Returns ``output`` after queueing everything: the caller's current
+    stream waits for the last copy, so synchronising that stream (or the device) makes ``output`` valid.
+    The reference has no host-memory entry point (its harness hands ``kernel`` device tensors)."""
+    for name, t in (("routing_logits", routing_logits), ("hidden_states", hidden_states),
+                    ("hidden_states_scale", hidden_states_scale)):
+        if not torch.is_tensor(t) or t.is_cuda or not t.is_pinned():
+            raise RuntimeError(f"{name} must be a pinned host tensor")
+    if routing_logits.dim() != 2:
+        raise ValueError("routing_logits must be [T, 256]")
+    T = int(routing_logits.shape[0])
+    logits = _require(routing_logits, "routing_logits", torch.float32, (T, E_GLOBAL))
+    hs = _require(hidden_states, "hidden_states", _FP8, (T, H))
+    hs_scale = _require(hidden_states_scale, "hidden_states_scale", torch.float32, (H_BLOCKS, T))
+    if output is None:
+        output = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    elif (not torch.is_tensor(output) or output.is_cuda or not output.is_pinned() or output.dtype != torch.bfloat16
+          or tuple(output.shape) != (T, H) or not output.is_contiguous()):
+        raise ValueError("output must be a contiguous pinned host bf16 tensor of shape [T, 7168]")
+    if T == 0:
+        return output
+    device = gemm1_weights.device
+    _require_cuda(gemm1_weights=gemm1_weights)
+    if slices is None:
+        # Every run streams the expert weights again (~E x 44 MB at ~5 TB/s) while the copies it can hide shrink with
+        # the number of runs (22.7 KB per token over a ~55 GB/s host link): the sum is least near sqrt(copy / stream).
+        # Measured at T = 16384 with 256 experts: 16.8 ms unsliced, 14.7 ms with 2 runs, 17.1 ms with 4.
+        stream_s = gemm1_weights.shape[0] * 44.04e6 / 5e12
+        copy_s = T * 22.7e3 / 55e9
+        slices = max(1, min(8, int(round((copy_s / stream_s) ** 0.5)), T // 1024))
+    if slices < 1 or slices > T:
+        raise ValueError("slices must be in 1..T")
+    if slices == 1:
+        # nothing to overlap: one copy in, the layer, one copy out, all on the caller's stream
+        with torch.cuda.device(device):
+            out_dev = kernel(logits.to(device, non_blocking=True), routing_bias, hs.to(device, non_blocking=True),
+                             hs_scale.to(device, non_blocking=True), gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                             gemm2_weights_scale, local_expert_offset, routed_scaling_factor)
+            output.copy_(out_dev, non_blocking=True)
+        return output
+    t_slice = (T + slices - 1) // slices
+    pipe = _host_pipe(device, T, t_slice)
+    cur = torch.cuda.current_stream(device)
+    h2d, d2h = pipe["h2d"], pipe["d2h"]
+    h2d.wait_stream(cur)     # earlier work on the caller's stream may still read the staging buffers
+    d2h.wait_stream(cur)
+    scale_dev = pipe["scale"].view(-1)[:H_BLOCKS * T].view(H_BLOCKS, T)
+    with torch.cuda.stream(h2d):
+        scale_dev.copy_(hs_scale, non_blocking=True)
+    done, drained = [], []
+    for i in range(slices):
+        a, b = i * t_slice, min(T, (i + 1) * t_slice)
+        n, k = b - a, i % 2
+        with torch.cuda.stream(h2d):
+            if i >= 2:
+                h2d.wait_event(done[i - 2])          # the layer on run i - 2 has finished reading staging set k
+            pipe["logits"][k][:n].copy_(logits[a:b], non_blocking=True)
+            pipe["hs"][k][:n].copy_(hs[a:b], non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(h2d)
+        cur.wait_event(arrived)
+        if i >= 2:
+            cur.wait_event(drained[i - 2])           # the copy-out of run i - 2 has finished reading out[k]
+        kernel(pipe["logits"][k][:n], routing_bias, pipe["hs"][k][:n], scale_dev[:, a:b].contiguous(), gemm1_weights,
+               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor,
+               pipe["out"][k][:n])
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        done.append(ev)
+        with torch.cuda.stream(d2h):
+            d2h.wait_event(ev)
+            output[a:b].copy_(pipe["out"][k][:n], non_blocking=True)
+            ev2 = torch.cuda.Event()
+            ev2.record(d2h)
+            drained.append(ev2)
+    cur.wait_stream(d2h)
+    return output
+
+
 @torch.no_grad()
 def quantize_activations(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 activations [T, 7168] -> (e4m3 [T, 7168], float32 scales [56, T]): the ``hidden_states`` /

@@ -1,4 +1,5 @@
-"""GPU, BASELINE.json's prefill sizes (T = 4096 and 16384, 32 local experts, skewed router): the oracle cannot run the
+"""GPU, BASELINE.json's prefill sizes (T = 4096 and 16384, 32 local experts, skewed router; and the bench's headline
+configuration, T = 16384 with all 256 experts local): the oracle cannot run the
 whole layer at these sizes in seconds, so parity is checked through size-independent properties —
   * routing and the complete sort metadata bit-exact against the oracle (both are cheap on the CPU);
   * a random sample of token rows against the oracle run on just those tokens (routing and experts are per token);
@@ -91,3 +92,40 @@ def test_permutation_scaling_and_sharding(setup):
     assert_close(parts[0] + parts[1], out.float(), atol=2e-2, rtol=1.6e-2, what="sum of expert shards")
     nonzero_rows = (out.float().abs().sum(dim=1) > 0).sum().item()
     assert nonzero_rows > T // 4
+
+
+def test_headline_configuration_all_experts_local(oracle):
+    """bench.py's N = 1 workload (T = 16384, 256 local experts, N(0,1) router: 131 072 pairs, every token sums eight
+    expert rows): metadata bit-exact, and sampled rows against the oracle.  The oracle gets only the experts the
+    sampled tokens use, renumbered 0..n-1 (it takes the routing as given through forward_from_topk)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fused_moe_b200 import kernel as K, synth
+    T, E = 16384, 256
+    inp = synth.make_inputs(T, E, seed=0, skew=False, device="cuda")
+    out = K.kernel(**inp)
+    K.check_status()
+    ws = K.last_workspace()
+    idx = ws.view("topk_idx", torch.int32, (T, 8)).cpu()
+    w = ws.view("topk_w", torch.float32, (T, 8)).cpu()
+    ridx, rw = oracle.route(inp["routing_logits"], inp["routing_bias"], 2.5)
+    assert torch.equal(idx, ridx) and torch.equal(w, rw)
+    s = oracle.sort(ridx, rw, E, 0)
+    n = s["total_blocks"] * 128
+    assert int(s["counts"].sum()) == T * 8
+    assert int(ws.view("total_blocks", torch.int32, (1,)).item()) == s["total_blocks"]
+    assert torch.equal(ws.view("counts", torch.int32, (E,)).cpu(), s["counts"])
+    assert torch.equal(ws.view("block_offsets", torch.int32, (E + 1,)).cpu(), s["block_offsets"])
+    assert torch.equal(ws.view("sorted_token_ids", torch.int32, (ws.struct.R_max,))[:n].cpu(), s["sorted_token_ids"])
+    assert torch.equal(ws.view("scatter_map", torch.int32, (T, 8)).cpu(), s["scatter_map"])
+    pick = torch.randint(0, T, (6,), generator=torch.Generator().manual_seed(5)).sort().values
+    used = torch.unique(ridx[pick]).tolist()
+    renumber = {e: i for i, e in enumerate(used)}
+    sub_idx = torch.tensor([[renumber[int(e)] for e in row] for row in ridx[pick]], dtype=torch.int32)
+    sel = torch.tensor(used, device="cuda")
+    ref32, ref16, pairs = oracle.forward_from_topk(
+        sub_idx, rw[pick], inp["hidden_states"][pick.to("cuda")], inp["hidden_states_scale"][:, pick.to("cuda")],
+        inp["gemm1_weights"][sel], inp["gemm1_weights_scale"][sel], inp["gemm2_weights"][sel],
+        inp["gemm2_weights_scale"][sel], 0)
+    assert pairs == 48
+    assert_close(out[pick.to("cuda")].float().cpu(), ref16.float(), what="sampled rows, 256 local experts")

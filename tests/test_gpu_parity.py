@@ -334,3 +334,21 @@ def test_quantize_activations_matches_generator(moe, T, heavy):
         moe.quantize_activations(x)           # float32 input
     with pytest.raises(ValueError):
         moe.quantize_activations(xb[:, :128])  # wrong width
+
+
+@pytest.mark.parametrize("T,slices", [(8192, None), (9001, 4), (300, None)])
+def test_host_memory_entry_point_equals_device_call(moe, T, slices):
+    """kernel_host (pinned host activations, copies pipelined over token slices) gives the bytes of kernel()."""
+    inp = gpu_inputs(T, 32, 0, 0, True)
+    want = moe.kernel(**inp).cpu()
+    host = {k: inp[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
+    args = dict(inp)
+    args.update(host)
+    got = moe.kernel_host(**args, slices=slices)
+    again = torch.empty((T, 7168), dtype=torch.bfloat16).pin_memory()
+    assert moe.kernel_host(**args, output=again, slices=slices) is again    # back to back on the same staging buffers
+    torch.cuda.synchronize()
+    moe.check_status()
+    assert got.is_pinned() and torch.equal(got, want) and torch.equal(again, want)
+    with pytest.raises(RuntimeError):
+        moe.kernel_host(**inp)    # device activations
