@@ -117,15 +117,22 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits_row
   my_w = __fmul_rn(__fdiv_rn(my_s, __fadd_rn(sum, 1e-20f)), scale_factor);
 }
 
-__global__ void __launch_bounds__(1024, 1)
+// One CTA routes 8 tokens (a quarter of a 32-token chunk), one warp each: a token costs ~1000-1500 instructions on its
+// warp, so a CTA per whole chunk kept 32 such warps on one SM (12 us of kernel time for 80 tokens with 145 SMs idle).
+// The quarter's 8 selection bits per local expert are byte `quarter` of the chunk's 32-bit mask word: the four CTAs of
+// a chunk write disjoint bytes, so the mask needs neither atomics nor clearing.  The grid covers whole chunks
+// (4 CTAs each), so every byte of every mask word is written even where the last chunk is ragged.
+constexpr int ROUTE_WARPS = 8;
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
 k_route(const float* __restrict__ logits, const uint16_t* __restrict__ bias, int T, float scale_factor,
         int local_offset, int E_local, int* __restrict__ topk_idx, float* __restrict__ topk_w,
         uint32_t* __restrict__ chunk_bits) {
   __shared__ uint32_t s_bits[E_GLOBAL];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int chunk = blockIdx.x;
-  const int t = chunk * 32 + warp;
+  const int chunk = blockIdx.x >> 2;
+  const int quarter = blockIdx.x & 3;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
 
   pdl_launch_dependents();
   if (threadIdx.x < E_GLOBAL) s_bits[threadIdx.x] = 0;
@@ -144,7 +151,10 @@ k_route(const float* __restrict__ logits, const uint16_t* __restrict__ bias, int
     }
   }
   __syncthreads();
-  if (threadIdx.x < E_local) chunk_bits[static_cast<size_t>(chunk) * E_local + threadIdx.x] = s_bits[threadIdx.x];
+  if (threadIdx.x < E_local) {
+    uint8_t* word = reinterpret_cast<uint8_t*>(chunk_bits + static_cast<size_t>(chunk) * E_local + threadIdx.x);
+    word[quarter] = static_cast<uint8_t>(s_bits[threadIdx.x]);   // little-endian: byte q = bits 8q .. 8q+7
+  }
 }
 
 // Small batches (T <= B200MOE_PROLOGUE_MAX_T): routing, ranking, padded layout, scatter and the activation gather in ONE launch instead of
@@ -323,7 +333,7 @@ k_topk_bits(const int* __restrict__ topk_idx, long long idx_stride, int T, int l
 
 int launch_route(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
-  B200MOE_CUDA_TRY(launch_pdl(k_route, dim3(ws->n_chunks), dim3(1024), 0, st, p->routing_logits, p->routing_bias, p->T,
+  B200MOE_CUDA_TRY(launch_pdl(k_route, dim3(ws->n_chunks * 4), dim3(ROUTE_WARPS * 32), 0, st, p->routing_logits, p->routing_bias, p->T,
                               p->routed_scaling_factor, p->local_expert_offset, p->E_local, ws->topk_idx, ws->topk_w,
                               ws->chunk_bits));
   return B200MOE_OK;

@@ -109,6 +109,8 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     (33, 32, 7, 32, False),    # first batch size on the separate route / sort / gather kernels
     (256, 32, 10, 0, True),    # largest batch on the token-minor GEMMs, experts with several 64-row sub-blocks
     (257, 32, 10, 0, True),    # first batch size on the 128-token-tile GEMMs
+    (1000, 32, 11, 0, True),   # 32 token chunks, ragged; experts with several 128-row blocks
+    (1025, 8, 11, 40, False),  # one token into the 33rd chunk
 ])
 def test_layer_matches_oracle(moe, oracle, T, E_local, seed, offset, skew):
     out, ref, _ = run_and_check(moe, oracle, T, E_local, seed, offset, skew)
