@@ -122,72 +122,103 @@ k_gemv2_reduce(const float* __restrict__ inter, const int* __restrict__ topk_idx
   __shared__ __align__(16) __half2 s_x[TOP_K][I / 2];   // 32 KB
   __shared__ float s_back[TOP_K];                       // weight * row maximum / 7
   __shared__ int s_e[TOP_K];
-  __shared__ float s_red[8];
+  __shared__ float s_red[TOP_K][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int CTAS_PER_TOKEN = H / GEMV2_N_PER_CTA;
   const int t = blockIdx.x / CTAS_PER_TOKEN;
   const int n0 = (blockIdx.x - t * CTAS_PER_TOKEN) * GEMV2_N_PER_CTA;
   pdl_launch_dependents();
   pdl_wait();
+  // Stage the token's local rows: all loads first (up to 8 rows x 8 floats per thread), one block-wide maximum for all
+  // rows at once, then the scaled f16 copies.  (Row by row this was a chain of 8 x (load, two barriers) before the first
+  // weight byte was requested.)
+  int e_k[TOP_K];
+  float4 v[TOP_K][2];
+  float m[TOP_K];
+#pragma unroll
   for (int k = 0; k < TOP_K; ++k) {
     const int p = t * TOP_K + k;
     const int e = __ldg(topk_idx + p) - local_offset;
-    const bool local = e >= 0 && e < E_local;   // CTA-uniform
-    if (threadIdx.x == 0) s_e[k] = local ? e : -1;
-    if (!local) continue;
-    const float4* x = reinterpret_cast<const float4*>(inter + static_cast<size_t>(p) * I);
-    float4 v[2];
-    float m = 0.f;
+    e_k[k] = (e >= 0 && e < E_local) ? e : -1;   // CTA-uniform
+    m[k] = 0.f;
+    if (e_k[k] >= 0) {
+      const float4* x = reinterpret_cast<const float4*>(inter + static_cast<size_t>(p) * I);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      v[j] = __ldg(x + threadIdx.x * 2 + j);   // 256 threads x 8 floats = 2048
-      m = fmaxf(m, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+      for (int j = 0; j < 2; ++j) v[k][j] = __ldg(x + threadIdx.x * 2 + j);   // 256 threads x 8 floats = 2048
     }
+  }
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-    if (lane == 0) s_red[warp] = m;
-    __syncthreads();
-    m = s_red[0];
+  for (int k = 0; k < TOP_K; ++k) {
+    if (e_k[k] < 0) continue;
 #pragma unroll
-    for (int j = 1; j < 8; ++j) m = fmaxf(m, s_red[j]);
-    const float r = m > 0.f ? 7.0f / m : 0.f;
+    for (int j = 0; j < 2; ++j)
+      m[k] = fmaxf(m[k], fmaxf(fmaxf(fabsf(v[k][j].x), fabsf(v[k][j].y)), fmaxf(fabsf(v[k][j].z), fabsf(v[k][j].w))));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m[k] = fmaxf(m[k], __shfl_xor_sync(0xffffffffu, m[k], d));
+    if (lane == 0) s_red[k][warp] = m[k];
+  }
+  if (threadIdx.x < TOP_K) s_e[threadIdx.x] = e_k[threadIdx.x];
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < TOP_K; ++k) {
+    if (e_k[k] < 0) continue;
+    float mk = s_red[k][0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mk = fmaxf(mk, s_red[k][j]);
+    const float r = mk > 0.f ? 7.0f / mk : 0.f;
     __half2* dst = &s_x[k][threadIdx.x * 4];
-    dst[0] = __floats2half2_rn(v[0].x * r, v[0].y * r);
-    dst[1] = __floats2half2_rn(v[0].z * r, v[0].w * r);
-    dst[2] = __floats2half2_rn(v[1].x * r, v[1].y * r);
-    dst[3] = __floats2half2_rn(v[1].z * r, v[1].w * r);
-    if (threadIdx.x == 0) s_back[k] = __ldg(topk_w + p) * m * (1.0f / 7.0f);
-    __syncthreads();   // s_red is reused by the next local pair
+    dst[0] = __floats2half2_rn(v[k][0].x * r, v[k][0].y * r);
+    dst[1] = __floats2half2_rn(v[k][0].z * r, v[k][0].w * r);
+    dst[2] = __floats2half2_rn(v[k][1].x * r, v[k][1].y * r);
+    dst[3] = __floats2half2_rn(v[k][1].z * r, v[k][1].w * r);
+    if (threadIdx.x == 0) s_back[k] = __ldg(topk_w + t * TOP_K + k) * mk * (1.0f / 7.0f);
   }
   __syncthreads();
-  for (int n = n0 + warp; n < n0 + GEMV2_N_PER_CTA; n += 8) {
-    float total = 0.f;   // per-lane share; lanes are added once per column, after all of the token's experts
-#pragma unroll 2
-    for (int k = 0; k < TOP_K; ++k) {
-      const int e = s_e[k];
-      if (e < 0) continue;
-      const uint4* w_row = reinterpret_cast<const uint4*>(w2 + (static_cast<size_t>(e) * H + n) * I);
-      const float* sc = w2_scale + (static_cast<size_t>(e) * H_BLOCKS + (n >> 7)) * I_BLOCKS;
-      float acc = 0.f;
+  // Each warp owns 4 output columns (n0 + warp + 8 j).  Per local expert it first requests all 16 weight loads of its
+  // four rows (2 KB each), then consumes them: 8 KB in flight per warp instead of 2.
+  constexpr int COLS = GEMV2_N_PER_CTA / 8;
+  float total[COLS];   // per-lane shares; lanes are added once per column, after all of the token's experts
 #pragma unroll
-      for (int i = 0; i < I / 16 / 32; ++i) {
-        const int c = i * 32 + lane;
-        const uint4 w = ld_stream(w_row + c);
-        Half2x8 a;
-        const uint4* sa = reinterpret_cast<const uint4*>(&s_x[k][c * 8]);
-        *reinterpret_cast<uint4*>(&a.v[0]) = sa[0];
-        *reinterpret_cast<uint4*>(&a.v[4]) = sa[1];
-        acc = fmaf(dot16_h2(a, w), __ldg(sc + (c >> 3)), acc);
-      }
-      total = fmaf(s_back[k], acc, total);
+  for (int j = 0; j < COLS; ++j) total[j] = 0.f;
+  for (int k = 0; k < TOP_K; ++k) {
+    const int e = s_e[k];
+    if (e < 0) continue;
+    const float* sc = w2_scale + (static_cast<size_t>(e) * H_BLOCKS + (n0 >> 7)) * I_BLOCKS;
+    uint4 w[COLS][I / 16 / 32];
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) {
+      const uint4* w_row = reinterpret_cast<const uint4*>(w2 + (static_cast<size_t>(e) * H + n0 + warp + 8 * j) * I);
+#pragma unroll
+      for (int i = 0; i < I / 16 / 32; ++i) w[j][i] = ld_stream(w_row + i * 32 + lane);
     }
-    total = warp_sum(total);
+    float acc[COLS];
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < I / 16 / 32; ++i) {
+      const int c = i * 32 + lane;
+      Half2x8 a;
+      const uint4* sa = reinterpret_cast<const uint4*>(&s_x[k][c * 8]);
+      *reinterpret_cast<uint4*>(&a.v[0]) = sa[0];
+      *reinterpret_cast<uint4*>(&a.v[4]) = sa[1];
+      const float scale = __ldg(sc + (c >> 3));
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) acc[j] = fmaf(dot16_h2(a, w[j][i]), scale, acc[j]);
+    }
+    const float back = s_back[k];
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) total[j] = fmaf(back, acc[j], total[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < COLS; ++j) {
+    const float sum = warp_sum(total[j]);
+    const int n = n0 + warp + 8 * j;
     if (lane == 0) {
       if (out) {
-        __nv_bfloat16 b = __float2bfloat16_rn(total);
+        __nv_bfloat16 b = __float2bfloat16_rn(sum);
         out[static_cast<size_t>(t) * H + n] = *reinterpret_cast<uint16_t*>(&b);
       }
-      if (out_f32) out_f32[static_cast<size_t>(t) * H + n] = total;
+      if (out_f32) out_f32[static_cast<size_t>(t) * H + n] = sum;
     }
   }
 }
