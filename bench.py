@@ -238,7 +238,7 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
         p.gemm2_weights, p.gemm2_weights_scale = inp["gemm2_weights"].data_ptr(), inp["gemm2_weights_scale"].data_ptr()
         p.output = out.data_ptr()
     res = {}
-    if records is None and T <= _lib.DECODE_MAX_T:
+    if records is None and _lib.uses_decode_path(T, E_local):
         names = ("route", "gemv1", "gemv2")          # decode path of b200moe_forward
     elif records is None and T <= _lib.PROLOGUE_MAX_T:
         names = ("prologue_small", "gemm1", "gemm2", "reduce")   # route + sort + gather are one launch here
@@ -342,7 +342,15 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     pos = [inp[k] for k in keys]
     # our kernels per step: route, rank-scan, scatter, gather, GEMM1, GEMM2, reduce; under expert parallelism the
     # dispatch adds dest-bits, rank-scan, slots, pack, the receiver swaps route for chunk-bits, combine adds one
-    launches_per_step = (3 if T_loc <= 2 else 7) if world == 1 else 13
+    from fused_moe_b200 import _lib as _l
+    if world > 1:
+        launches_per_step = 13
+    elif _l.uses_decode_path(T_loc, E_local):
+        launches_per_step = 3          # route, GEMV1, GEMV2
+    elif T_loc <= _l.PROLOGUE_MAX_T:
+        launches_per_step = 4          # fused prologue, GEMM1, GEMM2, reduce
+    else:
+        launches_per_step = 7
     if world == 1:
         def step():
             K.kernel(*pos, out)

@@ -338,7 +338,8 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   int sms;
   if ((rc = device_info(&sms))) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->routing_logits && p->T <= B200MOE_DECODE_MAX_T && p->out_seg_count == 0 && !p->hidden_row_stride &&
+  if (p->routing_logits && p->T <= B200MOE_DECODE_MAX_T && p->T * p->E_local <= B200MOE_DECODE_MAX_WORK &&
+      p->out_seg_count == 0 && !p->hidden_row_stride &&
       !p->scale_token_stride && !p->scale_block_stride) {
     // decode: a few tokens, one or two rows per expert — stream the weights through matrix-vector kernels
     if ((rc = launch_route(p, ws, st))) return rc;

@@ -39,7 +39,9 @@ extern "C" {
 #define B200MOE_GEMM_MAX_CTAS 160  /* CTAs of a token-minor GEMM launch (one per SM, at most this many) */
 #define B200MOE_SKINNY_MAX_T 256   /* b200moe_forward uses the token-minor GEMM kernels up to this batch size */
 #define B200MOE_PROLOGUE_MAX_T 32  /* largest batch of b200moe_prologue_small */
-#define B200MOE_DECODE_MAX_T 2 /* up to this many tokens b200moe_forward takes the matrix-vector (decode) path */
+#define B200MOE_DECODE_MAX_T 8 /* the matrix-vector (decode) stages take at most this many tokens; b200moe_forward
+                                  uses them while T * E_local <= B200MOE_DECODE_MAX_WORK */
+#define B200MOE_DECODE_MAX_WORK 256 /* = 8 expected (token, local expert) pairs: T * 8 * E_local / 256 */
 
 enum {
   B200MOE_OK = 0,
@@ -153,8 +155,8 @@ int b200moe_workspace_carve(void* base, size_t bytes, int32_t T, int32_t E_local
 int b200moe_workspace_init(const b200moe_workspace* ws /* host */, void* stream);
 
 /* Whole layer: route -> rank -> scatter -> gather -> GEMM1+SwiGLU -> GEMM2 -> weighted reduce, all on `stream`,
- * no host synchronisation.  With routing_logits given and T <= B200MOE_DECODE_MAX_T it runs route -> GEMV1+SwiGLU ->
- * GEMV2+reduce instead (b200moe_gemv1 / b200moe_gemv2 below): no sort, no gather, fp32 intermediate.  Replaces solution/python/pure_triton_impl.py:2125-2403 (kernel), :2025-2123 (_kernel_t1),
+ * no host synchronisation.  With routing_logits given, T <= B200MOE_DECODE_MAX_T and T * E_local <=
+ * B200MOE_DECODE_MAX_WORK it runs route -> GEMV1+SwiGLU -> GEMV2+reduce instead (b200moe_gemv1 / b200moe_gemv2 below): no sort, no gather, fp32 intermediate.  Replaces solution/python/pure_triton_impl.py:2125-2403 (kernel), :2025-2123 (_kernel_t1),
  * solution/python/triton_impl.py:346-566 and solution/python/triton_impl_t901.py:40-185. */
 int b200moe_forward(const b200moe_problem* p /* host */, const b200moe_workspace* ws /* host */, void* stream);
 

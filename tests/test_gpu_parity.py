@@ -70,8 +70,10 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     assert torch.equal(w, ref["topk_w"]), "routing weights differ from the oracle"
 
     # sort metadata: bit-exact, as the forward call left it (for 2 < T <= 32 that is the fused single-launch prologue,
-    # above it the separate sort kernels).  The decode path (T <= 2) does not sort, so the stage is run here explicitly.
-    if T <= 2:
+    # above it the separate sort kernels).  The decode path (few expected pairs) does not sort, so the stage is run here
+    # explicitly.
+    from fused_moe_b200._lib import uses_decode_path
+    if uses_decode_path(T, E_local):
         from fused_moe_b200 import _lib
         from fused_moe_b200.kernel import _problem
         p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]), inp["routing_logits"],
@@ -95,9 +97,13 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
 
 
 @pytest.mark.parametrize("T,E_local,seed,offset,skew", [
-    (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration
+    (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration (decode path: 7 expected pairs)
     (1, 32, 5, 96, False),     # decode path (matrix-vector kernels)
     (2, 32, 9, 0, False),      # decode path, two tokens
+    (8, 32, 14, 0, True),      # last batch size on the decode path for 32 local experts, skewed: shared experts
+    (9, 32, 14, 0, True),      # first batch size past it
+    (1, 256, 15, 0, False),    # all experts local: decode path for one token only (eight pairs)
+    (2, 256, 15, 0, False),    # all experts local, two tokens: fused prologue + token-minor GEMMs
     (80, 32, 1, 0, False),     # small batch
     (33, 8, 3, 60, False),     # E_local below one warp, non-zero offset, two token chunks
     (40, 3, 13, 253, True),    # last experts, skewed router
@@ -203,6 +209,10 @@ def test_token_minor_gemms_match_tile_gemms(moe, T, E_local, seed, offset, skew)
     p = _problem(T, E_local, offset, float(inp["routed_scaling_factor"]), inp["routing_logits"], inp["routing_bias"],
                  inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"],
                  inp["gemm2_weights"], inp["gemm2_weights_scale"], out)
+    # the sorted rows both GEMM pairs read (the forward call above may have taken the decode path, which does not sort)
+    for stage in ("route", "sort", "gather"):
+        _lib.check(getattr(lib, "b200moe_" + stage)(C.byref(p), C.byref(ws.struct), stream), stage)
+    torch.cuda.synchronize()
     rows = int(ws.view("total_blocks", torch.int32, (1,)).item()) * 128
     real = ws.view("sorted_token_ids", torch.int32, (R,))[:rows] < T
 
