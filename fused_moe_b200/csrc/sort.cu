@@ -191,7 +191,10 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
     s_w[threadIdx.x] = topk_w ? __ldg(topk_w + static_cast<size_t>(t) * w_stride + threadIdx.x) : 1.0f;
   }
   __syncthreads();
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  // gridDim.y CTAs share a token's 896 eight-column vectors (small batches: a token per CTA left most SMs idle and
+  // made each thread walk seven dependent rounds of loads)
+  const int per = (H / 8) / gridDim.y;
+  for (int v = blockIdx.y * per + threadIdx.x; v < (blockIdx.y + 1) * per; v += blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -225,6 +228,9 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   if (segs.count > 0) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
 }
 
+// CTAs per token of k_reduce: 7 x 128 threads = one vector per thread while the batch alone cannot fill the GPU
+static unsigned reduce_splits(int T) { return T <= 512 ? 7u : 1u; }
+
 // Entry points for the expert-parallel code (ep.cu), which ranks (token, destination) pairs with the same scan and adds
 // returned rows with the same reduce.
 int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* counts, cudaStream_t st) {
@@ -233,7 +239,7 @@ int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* 
 }
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
   OutSegments none = {};
-  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
                               static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none));
   return B200MOE_OK;
 }
@@ -279,7 +285,7 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   segs.count = p->out_seg_count;
   for (int i = 0; i < 8; ++i) segs.base[i] = p->out_seg_base[i];
   for (int i = 0; i < 9; ++i) segs.start[i] = p->out_seg_start[i];
-  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
                               p->output, p->output_f32, segs));
   return B200MOE_OK;
