@@ -490,7 +490,7 @@ def run_ours(args):
             "layer_roofline": {"bound": lr["bound"], "frac": round(lr["frac"], 4), "t_roof_us": round(lr["t_roof_us"], 1)},
             "ep_phase_us_rank0": rec.get("ep_phase_us"), "cpu_baseline": cpu, "sweep": sweep,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
@@ -557,11 +557,30 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """Writes the one JSON line to the process's real stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
+    global _RESULT_FD
     args = parse_args()
+    # stdout carries exactly one JSON line, but libraries write to file descriptor 1 on their own (NCCL prints its
+    # version banner there whatever NCCL_DEBUG says): keep the real stdout aside and point fd 1 at stderr for the run
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
