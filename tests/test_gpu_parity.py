@@ -364,3 +364,19 @@ def test_host_memory_entry_point_equals_device_call(moe, T, slices):
     assert got.is_pinned() and torch.equal(got, want) and torch.equal(again, want)
     with pytest.raises(RuntimeError):
         moe.kernel_host(**inp)    # device activations
+
+
+def test_interleaved_batch_sizes_share_one_workspace(moe):
+    """Calls of different batch sizes alternate on one device (one shared scratch buffer, re-carved per size; every
+    dispatch class of b200moe_forward; tile tickets that must be back at zero): each repeats its first result bit for
+    bit, without any synchronisation between the calls."""
+    sizes = [1, 7, 9, 16, 33, 80, 256, 300, 1000]
+    inputs = {T: gpu_inputs(T, 32, 0, 0, True) for T in sizes}
+    first = {T: moe.kernel(**inputs[T]).clone() for T in sizes}
+    torch.cuda.synchronize()
+    order = torch.randint(0, len(sizes), (40,), generator=torch.Generator().manual_seed(3)).tolist()
+    outs = [(sizes[i], moe.kernel(**inputs[sizes[i]]).clone()) for i in order]
+    torch.cuda.synchronize()
+    moe.check_status()
+    for T, out in outs:
+        assert torch.equal(out, first[T]), f"T={T} changed between calls"
