@@ -21,6 +21,7 @@ struct GemmArgs {
   float* partial;            // token-minor kernels: partial sums of shared tiles, two slots per CTA
   int E_local;
   int R_max;
+  int early_weights;         // token-minor GEMM2 launched right behind token-minor GEMM1: see gemm_skinny.cu
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {

@@ -312,7 +312,13 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const int E = args.E_local;
   constexpr int NT = C::N_TILES;
 
-  pdl_launch_dependents();
+  // GEMM2 behind GEMM1 in b200moe_forward (args.early_weights): its weights do not depend on GEMM1, and the sort
+  // metadata it needs was complete before GEMM1 passed its own dependency wait.  GEMM1 therefore releases its dependents
+  // only AFTER that wait, and GEMM2 reads the metadata and starts its weight loaders BEFORE its wait; only the roles
+  // that touch what GEMM1 writes (token tiles, scales, tickets, partial sums) wait.  The first stages of W2 are then in
+  // flight while the slowest GEMM1 CTAs still finish.
+  const bool early = (MODE == 2) && args.early_weights != 0;
+  if (MODE == 2) pdl_launch_dependents();
   if (threadIdx.x == 0) aux->abort_flag = 0;
   if (warp == PRODUCER_WARP && lane == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -335,7 +341,8 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     tmem_relinquish();
   }
   // CTA-local set-up above may overlap the tail of the previous kernel; what that kernel wrote is read from here on
-  pdl_wait();
+  if (!early) pdl_wait();
+  if (MODE == 1) pdl_launch_dependents();
   for (int i = threadIdx.x; i <= E; i += THREADS) aux->off[i] = __ldg(args.block_offsets + i);
   for (int i = threadIdx.x; i < E; i += THREADS) aux->cnt[i] = __ldg(args.counts + i);
   __syncthreads();
@@ -384,6 +391,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     if (warp == PRODUCER_WARP) {
       // ------------------------------------------------------------------ TMA producer (one thread)
       if (lane == 0) {
+        if (early) pdl_wait();   // the token tiles are GEMM1's output
         int stage = 0;
         uint32_t phase = 0;
         long long issued = 0;
@@ -539,6 +547,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #endif
   } else {
     setmaxnreg_inc<224>();
+    if (early) pdl_wait();   // scales, tickets and partial-sum slots are GEMM1's
     // ------------------------------------------------------------------ promotion + epilogue (8 warps)
     PromoState ps;
     bool ok = true;
@@ -566,7 +575,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 }
 
 template <int MODE>
-static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st, bool early) {
   if (p->T == 0) return B200MOE_OK;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -590,6 +599,7 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
   a.R_max = ws->R_max;
   a.tile_ctr = ws->gemm_tile_ctr;
   a.partial = ws->gemm_partial;
+  a.early_weights = early ? 1 : 0;
   a.weights = static_cast<const uint8_t*>(MODE == 1 ? p->gemm1_weights : p->gemm2_weights);
   if (!a.tile_ctr || !a.partial) return B200MOE_EWORKSPACE;
   if (MODE == 1) {
@@ -611,10 +621,12 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
 }  // namespace skinny
 
 int launch_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
-  return skinny::launch<1>(p, ws, num_sms, st);
+  return skinny::launch<1>(p, ws, num_sms, st, false);
 }
-int launch_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
-  return skinny::launch<2>(p, ws, num_sms, st);
+// behind_gemm1: the launch directly follows launch_gemm1_skinny on the same stream and workspace
+int launch_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,
+                        bool behind_gemm1) {
+  return skinny::launch<2>(p, ws, num_sms, st, behind_gemm1);
 }
 
 }  // namespace b200moe
