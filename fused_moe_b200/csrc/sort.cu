@@ -55,18 +55,39 @@ k_rank_scan(const uint32_t* __restrict__ chunk_bits, int n_chunks, int E_local, 
 }
 
 // Padded layout (every CTA recomputes it in shared memory; CTA 0 publishes it) and the scatter, one warp per chunk.
+// SCAN = true (batches of at most 32 chunks): the CTA also derives the per-expert totals and the prefix for its four
+// chunks from the bit matrix itself (at most 32 x E words, read with coalesced loads), so k_rank_scan is not launched
+// and chunk_base is not used; CTA 0 publishes counts.
+constexpr int SCATTER_SCAN_MAX_CHUNKS = 32;
+template <bool SCAN>
 __global__ void __launch_bounds__(128)
 k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, long long topk_stride,
           const uint32_t* __restrict__ chunk_bits,
-          const int* __restrict__ chunk_base, const int* __restrict__ counts, int T, int local_offset, int E_local,
+          const int* __restrict__ chunk_base, int* __restrict__ counts, int T, int local_offset, int E_local,
           int n_chunks, int* __restrict__ block_offsets, int* __restrict__ total_blocks,
           int* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights, int* __restrict__ scatter_map) {
   __shared__ int s_row_base[E_GLOBAL + 1];
+  __shared__ int s_cnt[SCAN ? E_GLOBAL : 1];
+  __shared__ int s_base[SCAN ? 4 : 1][SCAN ? E_GLOBAL : 1];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
 
   pdl_launch_dependents();
   pdl_wait();
+  if (SCAN) {
+    const int c_first = blockIdx.x * 4;
+    for (int e = threadIdx.x; e < E_local; e += blockDim.x) {
+      int run = 0;
+#pragma unroll 8
+      for (int c = 0; c < n_chunks; ++c) {
+        if (c >= c_first && c < c_first + 4) s_base[c - c_first][e] = run;
+        run += __popc(__ldg(chunk_bits + static_cast<size_t>(c) * E_local + e));
+      }
+      s_cnt[e] = run;
+      if (blockIdx.x == 0) counts[e] = run;
+    }
+    __syncthreads();
+  }
   if (warp == 0) {
     // lane handles experts [8*lane, 8*lane+8)
     int blocks[8];
@@ -74,7 +95,7 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, lo
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       int e = lane * 8 + i;
-      int c = (e < E_local) ? __ldg(counts + e) : 0;
+      int c = (e < E_local) ? (SCAN ? s_cnt[e] : __ldg(counts + e)) : 0;
       blocks[i] = (c + BLOCK_M - 1) / BLOCK_M;
       local += blocks[i];
     }
@@ -102,7 +123,7 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, lo
   }
   // pad rows: expert e is handled by CTA (e mod gridDim)
   for (int e = blockIdx.x; e < E_local; e += gridDim.x) {
-    int begin = s_row_base[e] * BLOCK_M + __ldg(counts + e);
+    int begin = s_row_base[e] * BLOCK_M + (SCAN ? s_cnt[e] : __ldg(counts + e));
     int end = s_row_base[e + 1] * BLOCK_M;
     for (int r = begin + threadIdx.x; r < end; r += blockDim.x) {
       sorted_token_ids[r] = T;
@@ -122,7 +143,8 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, lo
     dest[k] = -1;
     if (le >= 0 && le < E_local) {
       uint32_t bits = __ldg(chunk_bits + static_cast<size_t>(chunk) * E_local + le);
-      int rank = __ldg(chunk_base + static_cast<size_t>(chunk) * E_local + le) + __popc(bits & below);
+      int rank = (SCAN ? s_base[warp][le] : __ldg(chunk_base + static_cast<size_t>(chunk) * E_local + le)) +
+                 __popc(bits & below);
       int d = s_row_base[le] * BLOCK_M + rank;
       dest[k] = d;
       sorted_token_ids[d] = t;
@@ -254,13 +276,22 @@ int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStrea
     return B200MOE_OK;
   }
   const long long tstride = (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : TOP_K;
+  int grid = (ws->n_chunks + 3) / 4;
+  if (ws->n_chunks <= SCATTER_SCAN_MAX_CHUNKS) {
+    // small batch: the scatter CTAs do the scan themselves, one launch less
+    B200MOE_CUDA_TRY(launch_pdl(k_scatter<true>, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits,
+                                ws->chunk_base, ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks,
+                                ws->block_offsets, ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights,
+                                ws->scatter_map));
+    return B200MOE_OK;
+  }
   int scan_grid = (p->E_local + 31) / 32;
   B200MOE_CUDA_TRY(launch_pdl(k_rank_scan, dim3(scan_grid), dim3(1024), 0, st, ws->chunk_bits, ws->n_chunks, p->E_local,
                               ws->chunk_base, ws->counts));
-  int grid = (ws->n_chunks + 3) / 4;
-  B200MOE_CUDA_TRY(launch_pdl(k_scatter, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits, ws->chunk_base,
-                              ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks, ws->block_offsets,
-                              ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights, ws->scatter_map));
+  B200MOE_CUDA_TRY(launch_pdl(k_scatter<false>, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits,
+                              ws->chunk_base, ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks,
+                              ws->block_offsets, ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights,
+                              ws->scatter_map));
   return B200MOE_OK;
 }
 
