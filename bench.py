@@ -349,6 +349,8 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
         launches_per_step = 3          # route, GEMV1, GEMV2
     elif T_loc <= _l.PROLOGUE_MAX_T:
         launches_per_step = 4          # fused prologue, GEMM1, GEMM2, reduce
+    elif T_loc <= 1024:
+        launches_per_step = 6          # route, scatter (with the rank scan inside), gather, GEMM1, GEMM2, reduce
     else:
         launches_per_step = 7
     if world == 1:
