@@ -132,3 +132,19 @@ def test_synth_is_reproducible_and_shaped():
     deq = a["hidden_states"].float().view(5, 56, 128) * a["hidden_states_scale"].t().unsqueeze(2)
     assert deq.abs().max() < 6 and 0.8 < deq.std() < 1.2
     assert a["hidden_states"].float().abs().max() <= 448
+
+
+def test_documented_binding_matches_the_header_mirror():
+    """The ctypes structures printed in INTEGRATION.md (what a maintainer of the reference would paste) have the fields
+    and sizes of the package's own mirrors of b200moe_problem / b200moe_workspace."""
+    import ctypes as C
+    from pathlib import Path
+    from fused_moe_b200 import _lib
+    text = (Path(__file__).resolve().parent.parent / "INTEGRATION.md").read_text()
+    code = text[text.index("class Problem(C.Structure)"):text.index("_lib.b200moe_workspace_bytes.argtypes")]
+    ns = {"C": C}
+    exec(code, ns)
+    for name in ("Problem", "Workspace"):
+        doc, own = ns[name], getattr(_lib, name)
+        assert [f[0] for f in doc._fields_] == [f[0] for f in own._fields_]
+        assert C.sizeof(doc) == C.sizeof(own)
