@@ -118,7 +118,8 @@ typedef struct b200moe_workspace {
   int32_t* topk_idx;         /* [T,8]   global expert ids, descending biased score, ties to the lower id */
   float* topk_w;             /* [T,8]   s_k / (sum_k s_k + 1e-20) * routed_scaling_factor */
   uint32_t* chunk_bits;      /* [n_chunks, E_local] bit j set: token 32*chunk+j selected local expert e */
-  int32_t* chunk_base;       /* [n_chunks, E_local] pairs of expert e in earlier chunks */
+  int32_t* chunk_base;       /* [n_chunks, E_local] pairs of expert e in earlier chunks (scratch between the scan and
+                                the scatter; not written when n_chunks <= 32, where the scatter scans by itself) */
   int32_t* counts;           /* [E_local] */
   int32_t* block_offsets;    /* [E_local+1] */
   int32_t* total_blocks;     /* [1] */
