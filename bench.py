@@ -40,6 +40,7 @@ WORKLOADS = {
     # name: (T_global, local experts at N=1, skewed router)
     "prefill_ep": (16384, 256, False),
     "prefill_e32": (16384, 32, True),
+    "prefill14107_e32": (14107, 32, True),   # a batch size for which the reference publishes its CuTe-path time
     "prefill4096_e32": (4096, 32, True),
     "small_e32": (80, 32, False),
     "decode_e32": (1, 32, False),
@@ -457,7 +458,7 @@ def run_ours(args):
         if not args.no_sweep:
             del inp
             torch.cuda.empty_cache()
-            for name in ("decode_e32", "small_e32", "prefill4096_e32", "prefill_e32"):
+            for name in ("decode_e32", "small_e32", "prefill4096_e32", "prefill14107_e32", "prefill_e32"):
                 if name == args.workload:
                     continue
                 Tg, E, sk = WORKLOADS[name]
