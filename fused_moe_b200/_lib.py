@@ -24,7 +24,7 @@ def uses_decode_path(T: int, E_local: int) -> bool:
     return T <= DECODE_MAX_T and T * E_local <= DECODE_MAX_WORK
 
 PROLOGUE_MAX_T = 32
-SKINNY_MAX_T = 256
+SKINNY_MAX_T = 112
 
 
 class Problem(C.Structure):

@@ -37,7 +37,9 @@ extern "C" {
 #define B200MOE_QBLOCK 128
 #define B200MOE_BLOCK_M 128 /* rows per expert tile; every expert segment is padded to a multiple of this */
 #define B200MOE_GEMM_MAX_CTAS 160  /* CTAs of a token-minor GEMM launch (one per SM, at most this many) */
-#define B200MOE_SKINNY_MAX_T 256   /* b200moe_forward uses the token-minor GEMM kernels up to this batch size */
+#ifndef B200MOE_SKINNY_MAX_T
+#define B200MOE_SKINNY_MAX_T 112   /* b200moe_forward uses the token-minor GEMM kernels up to this batch size */
+#endif
 #define B200MOE_PROLOGUE_MAX_T 32  /* largest batch of b200moe_prologue_small */
 #define B200MOE_DECODE_MAX_T 8 /* the matrix-vector (decode) stages take at most this many tokens; b200moe_forward
                                   uses them while T * E_local <= B200MOE_DECODE_MAX_WORK */

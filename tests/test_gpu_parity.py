@@ -113,8 +113,9 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
     (32, 32, 7, 32, False),    # largest batch of the fused prologue: one full token chunk
     (31, 256, 8, 0, True),     # fused prologue, ragged chunk, every pair local (248 gathered rows)
     (33, 32, 7, 32, False),    # first batch size on the separate route / sort / gather kernels
-    (256, 32, 10, 0, True),    # largest batch on the token-minor GEMMs, experts with several 64-row sub-blocks
-    (257, 32, 10, 0, True),    # first batch size on the 128-token-tile GEMMs
+    (112, 32, 10, 0, True),    # largest batch on the token-minor GEMMs, experts with more than one 64-row sub-block
+    (113, 32, 10, 0, True),    # first batch size on the 128-token-tile GEMMs
+    (256, 32, 10, 0, True),    # eight full token chunks
     (1000, 32, 11, 0, True),   # 32 token chunks, ragged; experts with several 128-row blocks
     (1025, 8, 11, 40, False),  # one token into the 33rd chunk
 ])
@@ -370,7 +371,7 @@ def test_interleaved_batch_sizes_share_one_workspace(moe):
     """Calls of different batch sizes alternate on one device (one shared scratch buffer, re-carved per size; every
     dispatch class of b200moe_forward; tile tickets that must be back at zero): each repeats its first result bit for
     bit, without any synchronisation between the calls."""
-    sizes = [1, 7, 9, 16, 33, 80, 256, 300, 1000]
+    sizes = [1, 7, 9, 16, 33, 80, 112, 256, 300, 1000]
     inputs = {T: gpu_inputs(T, 32, 0, 0, True) for T in sizes}
     first = {T: moe.kernel(**inputs[T]).clone() for T in sizes}
     torch.cuda.synchronize()
