@@ -15,12 +15,12 @@ OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EUNSUPPORTED, ETOOLARGE = 0, -1, -2, -3,
 SORT_STATIC_MAX_ENTRIES = 32768
 EP_RECORD_BYTES = 7456
 DECODE_MAX_T = 8
-DECODE_MAX_WORK = 256
+DECODE_MAX_WORK = 128
 
 
 def uses_decode_path(T: int, E_local: int) -> bool:
     """Whether b200moe_forward takes the matrix-vector stages for a routed call with dense inputs (the weights are then
-    streamed once per (token, expert) pair, which wins while pairs rarely share an expert: about 8 expected pairs)."""
+    streamed once per (token, expert) pair, which wins while pairs rarely share an expert: about 4 expected pairs)."""
     return T <= DECODE_MAX_T and T * E_local <= DECODE_MAX_WORK
 
 PROLOGUE_MAX_T = 32

@@ -43,7 +43,7 @@ extern "C" {
 #define B200MOE_PROLOGUE_MAX_T 32  /* largest batch of b200moe_prologue_small */
 #define B200MOE_DECODE_MAX_T 8 /* the matrix-vector (decode) stages take at most this many tokens; b200moe_forward
                                   uses them while T * E_local <= B200MOE_DECODE_MAX_WORK */
-#define B200MOE_DECODE_MAX_WORK 256 /* = 8 expected (token, local expert) pairs: T * 8 * E_local / 256 */
+#define B200MOE_DECODE_MAX_WORK 128 /* = 4 expected (token, local expert) pairs: T * 8 * E_local / 256 */
 
 enum {
   B200MOE_OK = 0,

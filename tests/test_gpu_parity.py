@@ -97,13 +97,15 @@ def run_and_check(moe, oracle, T, E_local, seed, offset, skew, poison=True):
 
 
 @pytest.mark.parametrize("T,E_local,seed,offset,skew", [
-    (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration (decode path: 7 expected pairs)
+    (7, 32, 0, 0, False),      # the reference's CPU-runnable configuration
     (1, 32, 5, 96, False),     # decode path (matrix-vector kernels)
     (2, 32, 9, 0, False),      # decode path, two tokens
-    (8, 32, 14, 0, True),      # last batch size on the decode path for 32 local experts, skewed: shared experts
-    (9, 32, 14, 0, True),      # first batch size past it
-    (1, 256, 15, 0, False),    # all experts local: decode path for one token only (eight pairs)
-    (2, 256, 15, 0, False),    # all experts local, two tokens: fused prologue + token-minor GEMMs
+    (4, 32, 14, 0, True),      # last batch size on the decode path for 32 local experts, skewed: shared experts
+    (5, 32, 14, 0, True),      # first batch size past it
+    (8, 16, 14, 32, True),     # decode path at its token limit (16 local experts)
+    (9, 8, 14, 32, True),      # nine tokens: never the decode path
+    (1, 256, 15, 0, False),    # all experts local, one token (eight pairs): fused prologue + token-minor GEMMs
+    (1, 128, 15, 64, False),   # 128 local experts: decode path for one token only
     (80, 32, 1, 0, False),     # small batch
     (33, 8, 3, 60, False),     # E_local below one warp, non-zero offset, two token chunks
     (40, 3, 13, 253, True),    # last experts, skewed router
