@@ -54,6 +54,7 @@ class Problem(C.Structure):
         ("out_seg_count", C.c_int32),
         ("out_seg_start", C.c_int32 * 9),
         ("out_seg_base", C.c_void_p * 8),
+        ("plan", C.c_void_p),
     ]
 
 
@@ -65,6 +66,26 @@ class EpPeers(C.Structure):
         ("rank", C.c_int32),
         ("recv_records", C.c_void_p * 8),
         ("flags", C.c_void_p * 8),
+        ("counts", C.c_void_p * 8),
+        ("back_rows", C.c_void_p * 8),
+        ("cap_recv", C.c_int32),
+        ("cap_back", C.c_int32),
+    ]
+
+
+class EpPlan(C.Structure):
+    """Mirror of ``b200moe_ep_plan`` (lives in device memory; this mirror is for reading it back in tests and tools)."""
+
+    _fields_ = [
+        ("ok", C.c_int32),
+        ("n_recv", C.c_int32),
+        ("n_send", C.c_int32),
+        ("seg_count", C.c_int32),
+        ("seg_start", C.c_int32 * 9),
+        ("dst_row0", C.c_int32 * 8),
+        ("reserved", C.c_int32),
+        ("seg_base", C.c_void_p * 8),
+        ("matrix", C.c_int32 * 64),
     ]
 
 
@@ -94,6 +115,7 @@ class Workspace(C.Structure):
         ("expert_out", C.c_void_p),
         ("gemm_tile_ctr", C.c_void_p),
         ("gemm_partial", C.c_void_p),
+        ("status_mirror", C.c_void_p),
     ]
 
 
@@ -109,6 +131,7 @@ SYMBOLS = {
     "b200moe_forward": (C.c_int, _PW),
     "b200moe_quantize_act": (C.c_int, (C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p)),
     "b200moe_route": (C.c_int, _PW),
+    "b200moe_route_topk": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p)),
     "b200moe_topk_bits": (C.c_int, _PW),
     "b200moe_sort": (C.c_int, _PW),
     "b200moe_gather": (C.c_int, _PW),
@@ -129,6 +152,11 @@ SYMBOLS = {
     "b200moe_ep_pack_peers": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.POINTER(EpPeers), C.POINTER(C.c_int32),
                                                            C.c_void_p, C.c_size_t, C.c_void_p)),
     "b200moe_ep_barrier": (C.c_int, (C.POINTER(EpPeers), C.c_int32, C.c_void_p, C.c_void_p)),
+    "b200moe_ep_exchange_counts": (C.c_int, (C.POINTER(EpPeers), C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+                                             C.c_void_p)),
+    "b200moe_ep_pack_peers_planned": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.POINTER(EpPeers), C.c_void_p,
+                                                                   C.c_void_p, C.c_size_t, C.c_void_p)),
+    "b200moe_set_wait_limit_cycles": (C.c_int, (C.c_int64,)),
     "b200moe_ep_combine": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),
 }

@@ -16,6 +16,7 @@ int record_cuda_error(cudaError_t e) {
 
 int launch_route(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_topk_bits(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
+int launch_route_topk(const float*, const uint16_t*, int, float, int*, float*, cudaStream_t);
 int launch_small_prologue(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_sort(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
@@ -112,6 +113,7 @@ static size_t layout(uint8_t* base, int T, int E, b200moe_workspace* w) {
     w->expert_out = reinterpret_cast<float*>(expert_out);
     w->gemm_tile_ctr = reinterpret_cast<int32_t*>(gemm_tile_ctr);
     w->gemm_partial = reinterpret_cast<float*>(gemm_partial);
+    w->status_mirror = nullptr;
   }
   return off;
 }
@@ -200,6 +202,16 @@ int b200moe_route(const b200moe_problem* p, const b200moe_workspace* ws, void* s
   int sms;
   if ((rc = device_info(&sms))) return rc;
   return launch_route(p, ws, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_route_topk(const float* routing_logits, const uint16_t* routing_bias, int32_t T,
+                       float routed_scaling_factor, int32_t* topk_idx, float* topk_w, void* stream) {
+  if (T < 0 || T > (1 << 24)) return B200MOE_EINVAL;
+  if (T > 0 && (!routing_logits || !routing_bias || !topk_idx || !topk_w)) return B200MOE_EINVAL;
+  int sms, rc;
+  if ((rc = device_info(&sms))) return rc;
+  return launch_route_topk(routing_logits, routing_bias, T, routed_scaling_factor, topk_idx, topk_w,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
@@ -307,7 +319,7 @@ int b200moe_gemv2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
-  if (p->T > 0 && p->out_seg_count == 0 &&
+  if (p->T > 0 && p->out_seg_count == 0 && !p->plan &&
       ((!p->output && !p->output_f32) || !aligned16(p->output) || !aligned16(p->output_f32)))
     return B200MOE_EINVAL;
   if (p->out_seg_count < 0 || p->out_seg_count > 8) return B200MOE_EINVAL;
@@ -321,8 +333,10 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   if (rc) return rc;
   if (p->T == 0) return B200MOE_OK;
   if (!p->hidden_states || !p->hidden_states_scale || !p->gemm1_weights || !p->gemm1_weights_scale ||
-      !p->gemm2_weights || !p->gemm2_weights_scale || (!p->output && !p->output_f32 && p->out_seg_count == 0))
+      !p->gemm2_weights || !p->gemm2_weights_scale ||
+      (!p->output && !p->output_f32 && p->out_seg_count == 0 && !p->plan))
     return B200MOE_EINVAL;
+  if (p->plan && p->routing_logits) return B200MOE_EINVAL;  // a device-side plan describes received records only
   if (!aligned16(p->hidden_states) || !aligned16(p->gemm1_weights) || !aligned16(p->gemm2_weights) ||
       !aligned16(p->output) || !aligned16(p->output_f32))
     return B200MOE_EINVAL;

@@ -130,11 +130,13 @@ struct PeerTargets {
 __global__ void __launch_bounds__(256)
 k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale,
                const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int T, const int* __restrict__ counts,
-               int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows, const PeerTargets peers) {
+               int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows, const PeerTargets peers,
+               const b200moe_ep_plan* __restrict__ plan) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   pdl_launch_dependents();
   pdl_wait();
+  if (plan && !plan->ok) return;   // the counts did not fit the buffers (or the exchange timed out): store nothing
   int total = 0;
   int seg[9];
 #pragma unroll
@@ -155,7 +157,8 @@ k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hid
 #pragma unroll
       for (int j = 1; j < 8; ++j)
         if (s >= seg[j]) d = j;
-      rec = peers.base[d] + static_cast<size_t>(peers.row0[d] + (s - seg[d])) * EP_RECORD;
+      const int row0 = plan ? plan->dst_row0[d] : peers.row0[d];
+      rec = peers.base[d] + static_cast<size_t>(row0 + (s - seg[d])) * EP_RECORD;
     }
     const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
     uint4* dst = reinterpret_cast<uint4*>(rec);
@@ -174,9 +177,12 @@ k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hid
 
 // Bounded all-rank barrier on flags mapped into every rank: publish `epoch`, then wait for everybody's.
 constexpr int ST_BARRIER_TIMEOUT = 2;
+constexpr int ST_PLAN_OVERFLOW = 3;
+static long long g_wait_limit_cycles = WAIT_LIMIT_CYCLES;   // host side: limit handed to the barrier kernels
+
 __global__ void __launch_bounds__(32)
 k_ep_barrier(const PeerTargets flags /* base[r] = rank r's int flags[world] */, int world, int rank, int epoch,
-             int* __restrict__ status) {
+             long long limit_cycles, int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x;
@@ -190,7 +196,7 @@ k_ep_barrier(const PeerTargets flags /* base[r] = rank r's int flags[world] */, 
     volatile int* mine = reinterpret_cast<volatile int*>(flags.base[rank]) + lane;
     const long long t0 = clock64();
     while (*mine < epoch) {
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit_cycles) {
         if (atomicCAS(status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
           status[1] = rank;
           status[2] = lane;
@@ -201,6 +207,99 @@ k_ep_barrier(const PeerTargets flags /* base[r] = rank r's int flags[world] */, 
     }
   }
   __threadfence_system();
+}
+
+// The count exchange: row `rank` of every rank's count matrix <- send_counts, the flag barrier above, then thread 0
+// turns this rank's (complete) matrix into the plan the following kernels read.  One CTA of 64 threads.
+struct ExchangeTargets {
+  int* flags[8];
+  int* counts[8];
+  float* back[8];
+};
+__global__ void __launch_bounds__(64)
+k_ep_exchange(const ExchangeTargets tg, const int* __restrict__ send_counts, int world, int rank, int epoch,
+              int cap_recv, int cap_back, long long limit_cycles, b200moe_ep_plan* __restrict__ plan,
+              int* __restrict__ status) {
+  __shared__ int s_timeout;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  if (tid == 0) s_timeout = 0;
+  if (tid < world * world) {
+    const int d = tid / world, j = tid - d * world;
+    volatile int* remote = reinterpret_cast<volatile int*>(tg.counts[d]) + rank * 8 + j;
+    *remote = __ldg(send_counts + j);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world) {
+    volatile int* remote = reinterpret_cast<volatile int*>(tg.flags[tid]) + rank;
+    *remote = epoch;
+  }
+  __threadfence_system();
+  if (tid < world) {
+    volatile int* mine = reinterpret_cast<volatile int*>(tg.flags[rank]) + tid;
+    const long long t0 = clock64();
+    while (*mine < epoch) {
+      if (clock64() - t0 > limit_cycles) {
+        if (atomicCAS(status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
+          status[1] = rank;
+          status[2] = tid;
+          status[3] = epoch;
+        }
+        s_timeout = 1;
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    volatile const int* m = reinterpret_cast<volatile const int*>(tg.counts[rank]);
+    int mm[8][8];
+    bool ok = s_timeout == 0;
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+#pragma unroll
+      for (int d = 0; d < 8; ++d) {
+        const int v = (s < world && d < world) ? m[s * 8 + d] : 0;
+        mm[s][d] = v;
+        if (v < 0) ok = false;
+      }
+    for (int x = 0; x < world && ok; ++x) {
+      long long col = 0, row = 0;
+      for (int y = 0; y < world; ++y) { col += mm[y][x]; row += mm[x][y]; }
+      if (col > cap_recv || row > cap_back) ok = false;
+    }
+    if (!ok && s_timeout == 0 && atomicCAS(status, ST_OK, ST_PLAN_OVERFLOW) == ST_OK) {
+      status[1] = rank;
+      status[2] = cap_recv;
+      status[3] = cap_back;
+    }
+    plan->ok = ok ? 1 : 0;
+    plan->seg_count = world;
+    plan->reserved = 0;
+    int n_recv = 0, n_send = 0;
+    for (int s = 0; s < 8; ++s) {
+      plan->seg_start[s] = n_recv;
+      int before_me = 0;   // rows rank s sends to the ranks before this one: its return buffer keeps them first
+      for (int d = 0; d < 8; ++d) {
+        if (d < rank) before_me += ok ? mm[s][d] : 0;
+        plan->matrix[s * 8 + d] = ok ? mm[s][d] : 0;
+      }
+      plan->seg_base[s] = (s < world) ? tg.back[s] + static_cast<size_t>(before_me) * H : nullptr;
+      if (ok && s < world) n_recv += mm[s][rank];
+    }
+    plan->seg_start[8] = n_recv;
+    for (int d = 0; d < 8; ++d) {
+      int r0 = 0;
+      for (int s = 0; s < rank; ++s) r0 += ok ? mm[s][d] : 0;
+      plan->dst_row0[d] = r0;
+      if (ok && d < world) n_send += mm[rank][d];
+    }
+    plan->n_recv = n_recv;
+    plan->n_send = n_send;
+  }
 }
 
 }  // namespace b200moe
@@ -247,12 +346,12 @@ int check_scratch(int32_t T, int32_t world, const void* scratch, size_t scratch_
 }
 int launch_pack(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
                 const float* hidden_states_scale, int32_t T, int32_t world, const Scratch& sc, uint8_t* send_rows,
-                const PeerTargets& peers, cudaStream_t st) {
+                const PeerTargets& peers, const b200moe_ep_plan* plan, cudaStream_t st) {
   long long max_pairs = static_cast<long long>(T) * (world < TOP_K ? world : TOP_K);
   int pgrid = static_cast<int>((max_pairs + 7) / 8);
   if (pgrid > 148 * 8) pgrid = 148 * 8;
   B200MOE_CUDA_TRY(launch_pdl(k_pack_records, dim3(pgrid), dim3(256), 0, st, hidden_states, hidden_states_scale,
-                              topk_idx, topk_w, T, sc.counts, world, sc.slot_token, send_rows, peers));
+                              topk_idx, topk_w, T, sc.counts, world, sc.slot_token, send_rows, peers, plan));
   return B200MOE_OK;
 }
 }  // namespace
@@ -289,7 +388,7 @@ int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint
     return B200MOE_EINVAL;
   PeerTargets none = {};
   return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, world, carve_scratch(scratch, T, world),
-                     send_rows, none, static_cast<cudaStream_t>(stream));
+                     send_rows, none, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
@@ -308,7 +407,51 @@ int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const ui
     tg.row0[d] = dst_row0[d];
   }
   return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, peers->world,
-                     carve_scratch(scratch, T, peers->world), nullptr, tg, static_cast<cudaStream_t>(stream));
+                     carve_scratch(scratch, T, peers->world), nullptr, tg, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                                  const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers,
+                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!peers || !plan || peers->world < 1 || peers->world > 8) return B200MOE_EINVAL;
+  int rc = check_scratch(T, peers->world, scratch, scratch_bytes);
+  if (rc || T == 0) return rc;
+  if (!topk_idx || !topk_w || !hidden_states || !hidden_states_scale) return B200MOE_EINVAL;
+  if (reinterpret_cast<uintptr_t>(hidden_states) & 15u) return B200MOE_EINVAL;
+  PeerTargets tg = {};
+  for (int d = 0; d < peers->world; ++d) {
+    if (!peers->recv_records[d] || (reinterpret_cast<uintptr_t>(peers->recv_records[d]) & 15u)) return B200MOE_EINVAL;
+    tg.base[d] = peers->recv_records[d];
+  }
+  return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, peers->world,
+                     carve_scratch(scratch, T, peers->world), nullptr, tg, plan, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers, const int32_t* send_counts, int32_t epoch,
+                               b200moe_ep_plan* plan, int32_t* status, void* stream) {
+  if (!peers || !send_counts || !plan || !status || peers->world < 1 || peers->world > 8 || peers->rank < 0 ||
+      peers->rank >= peers->world || peers->cap_recv < 0 || peers->cap_back < 0)
+    return B200MOE_EINVAL;
+  if (reinterpret_cast<uintptr_t>(plan) & 7u) return B200MOE_EINVAL;
+  ExchangeTargets tg = {};
+  for (int d = 0; d < peers->world; ++d) {
+    if (!peers->flags[d] || !peers->counts[d] || !peers->back_rows[d] ||
+        (reinterpret_cast<uintptr_t>(peers->back_rows[d]) & 15u))
+      return B200MOE_EINVAL;
+    tg.flags[d] = peers->flags[d];
+    tg.counts[d] = peers->counts[d];
+    tg.back[d] = peers->back_rows[d];
+  }
+  B200MOE_CUDA_TRY(launch_pdl(k_ep_exchange, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream), tg, send_counts,
+                              peers->world, peers->rank, epoch, peers->cap_recv, peers->cap_back, g_wait_limit_cycles,
+                              plan, status));
+  return B200MOE_OK;
+}
+
+int b200moe_set_wait_limit_cycles(int64_t cycles) {
+  if (cycles < 0) return B200MOE_EINVAL;
+  g_wait_limit_cycles = cycles == 0 ? WAIT_LIMIT_CYCLES : static_cast<long long>(cycles);
+  return B200MOE_OK;
 }
 
 int b200moe_ep_barrier(const b200moe_ep_peers* peers, int32_t epoch, int32_t* status, void* stream) {
@@ -320,7 +463,7 @@ int b200moe_ep_barrier(const b200moe_ep_peers* peers, int32_t epoch, int32_t* st
     fl.base[d] = reinterpret_cast<uint8_t*>(peers->flags[d]);
   }
   B200MOE_CUDA_TRY(launch_pdl(k_ep_barrier, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), fl, peers->world,
-                              peers->rank, epoch, status));
+                              peers->rank, epoch, g_wait_limit_cycles, status));
   return B200MOE_OK;
 }
 

@@ -10,8 +10,8 @@
 // Layout: lane l holds experts {l, l+32, ..., l+224}, so register slot g of every lane belongs to routing group g.
 // Group top-2 and the global arg-max are REDUX (warp reduce) operations on order-preserving integer keys.
 //
-// One CTA = 32 warps = one 32-token chunk; the CTA also records, per local expert, which of its tokens selected it
-// (chunk_bits), which the stable ranking in sort.cu consumes.
+// One CTA = 8 warps = a quarter of a 32-token chunk; the CTA also records, per local expert, which of its tokens
+// selected it (its byte of the chunk's chunk_bits words), which the stable ranking in sort.cu consumes.
 #include "common.cuh"
 
 namespace b200moe {
@@ -296,12 +296,13 @@ k_small_prologue(const float* __restrict__ logits, const uint16_t* __restrict__ 
 // chunk_bits from an existing topk_idx: one warp per 32-token chunk, lane = token.
 __global__ void __launch_bounds__(128)
 k_topk_bits(const int* __restrict__ topk_idx, long long idx_stride, int T, int local_offset, int E_local, int n_chunks,
-            uint32_t* __restrict__ chunk_bits) {
+            uint32_t* __restrict__ chunk_bits, const b200moe_ep_plan* __restrict__ plan) {
   const int lane = threadIdx.x & 31;
   const int chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   pdl_launch_dependents();
   pdl_wait();
   if (chunk >= n_chunks) return;
+  if (plan) T = min(T, plan->n_recv);   // rows past the received count hold stale records: they select nothing
   const int t = chunk * 32 + lane;
   uint32_t mask[E_GLOBAL / 32];
 #pragma unroll
@@ -339,7 +340,18 @@ int launch_route(const b200moe_problem* p, const b200moe_workspace* ws, cudaStre
   return B200MOE_OK;
 }
 
-// route + sort + gather for T <= 128 in one launch (dense inputs only)
+// Routing alone into caller-owned arrays (no workspace, no selection bits): what an expert-parallel rank runs on its own
+// tokens before dispatch.
+int launch_route_topk(const float* logits, const uint16_t* bias, int T, float scale, int* topk_idx, float* topk_w,
+                      cudaStream_t st) {
+  if (T == 0) return B200MOE_OK;
+  const int n_chunks = (T + 31) / 32;
+  B200MOE_CUDA_TRY(launch_pdl(k_route, dim3(n_chunks * 4), dim3(ROUTE_WARPS * 32), 0, st, logits, bias, T, scale, 0, 0,
+                              topk_idx, topk_w, static_cast<uint32_t*>(nullptr)));
+  return B200MOE_OK;
+}
+
+// route + sort + gather for T <= B200MOE_PROLOGUE_MAX_T in one launch (dense inputs only)
 int launch_small_prologue(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
   // one CTA per 32 (token, k) pairs of the batch, at most 32
@@ -358,7 +370,7 @@ int launch_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, cuda
   const int* idx = p->routing_logits ? ws->topk_idx : p->topk_idx_in;
   B200MOE_CUDA_TRY(launch_pdl(k_topk_bits, dim3(grid), dim3(128), 0, st, idx,
                               p->topk_row_stride ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T, p->local_expert_offset, p->E_local,
-                              ws->n_chunks, ws->chunk_bits));
+                              ws->n_chunks, ws->chunk_bits, p->plan));
   return B200MOE_OK;
 }
 

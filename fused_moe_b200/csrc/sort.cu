@@ -65,7 +65,8 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, lo
           const uint32_t* __restrict__ chunk_bits,
           const int* __restrict__ chunk_base, int* __restrict__ counts, int T, int local_offset, int E_local,
           int n_chunks, int* __restrict__ block_offsets, int* __restrict__ total_blocks,
-          int* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights, int* __restrict__ scatter_map) {
+          int* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights, int* __restrict__ scatter_map,
+          const b200moe_ep_plan* __restrict__ plan) {
   __shared__ int s_row_base[E_GLOBAL + 1];
   __shared__ int s_cnt[SCAN ? E_GLOBAL : 1];
   __shared__ int s_base[SCAN ? 4 : 1][SCAN ? E_GLOBAL : 1];
@@ -134,7 +135,8 @@ k_scatter(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, lo
   const int chunk = blockIdx.x * (blockDim.x >> 5) + warp;
   if (chunk >= n_chunks) return;
   const int t = chunk * 32 + lane;
-  if (t >= T) return;
+  // with a device-side plan only the received rows exist; pad rows keep the id T (the capacity) either way
+  if (t >= (plan ? min(T, plan->n_recv) : T)) return;
   const uint32_t below = (1u << lane) - 1u;
   int dest[TOP_K];
 #pragma unroll
@@ -192,7 +194,8 @@ struct OutSegments {
 // (the expert-parallel combine adds rows that are already weighted).
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
-         long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs) {
+         long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
+         const b200moe_ep_plan* __restrict__ plan, const int* __restrict__ status, int* __restrict__ status_mirror) {
   const int t = blockIdx.x;
   float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr;
   if (segs.count > 0) {
@@ -208,6 +211,25 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   __shared__ float s_w[TOP_K];
   pdl_launch_dependents();
   pdl_wait();
+  // This is the last kernel of a layer call: if an earlier kernel of the call gave up on a wait, copy the status word
+  // to the host-visible mirror (plain stores into mapped host memory), where the host sees it without synchronising.
+  if (status_mirror && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && status[0] != 0) {
+    status_mirror[1] = status[1];
+    status_mirror[2] = status[2];
+    status_mirror[3] = status[3];
+    __threadfence_system();
+    status_mirror[0] = status[0];
+  }
+  if (plan) {
+    // the row window and the destinations were decided on the device (expert-parallel receiver)
+    if (t >= plan->n_recv) return;
+    int i = 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+      if (j < plan->seg_count && t >= plan->seg_start[j]) i = j;
+    out = nullptr;
+    dst_row = plan->seg_base[i] + static_cast<size_t>(t - plan->seg_start[i]) * H;
+  }
   if (threadIdx.x < TOP_K) {
     s_pos[threadIdx.x] = __ldg(scatter_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
     s_w[threadIdx.x] = topk_w ? __ldg(topk_w + static_cast<size_t>(t) * w_stride + threadIdx.x) : 1.0f;
@@ -247,7 +269,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
-  if (segs.count > 0) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
+  if (segs.count > 0 || plan) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
 }
 
 // CTAs per token of k_reduce: 7 x 128 threads = one vector per thread while the batch alone cannot fill the GPU
@@ -262,7 +284,9 @@ int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* 
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
   OutSegments none = {};
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
-                              static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none));
+                              static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none,
+                              static_cast<const b200moe_ep_plan*>(nullptr), static_cast<const int*>(nullptr),
+                              static_cast<int*>(nullptr)));
   return B200MOE_OK;
 }
 
@@ -282,7 +306,7 @@ int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStrea
     B200MOE_CUDA_TRY(launch_pdl(k_scatter<true>, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits,
                                 ws->chunk_base, ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks,
                                 ws->block_offsets, ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights,
-                                ws->scatter_map));
+                                ws->scatter_map, p->plan));
     return B200MOE_OK;
   }
   int scan_grid = (p->E_local + 31) / 32;
@@ -291,7 +315,7 @@ int launch_sort(const b200moe_problem* p, const b200moe_workspace* ws, cudaStrea
   B200MOE_CUDA_TRY(launch_pdl(k_scatter<false>, dim3(grid), dim3(128), 0, st, idx, w, tstride, ws->chunk_bits,
                               ws->chunk_base, ws->counts, p->T, p->local_expert_offset, p->E_local, ws->n_chunks,
                               ws->block_offsets, ws->total_blocks, ws->sorted_token_ids, ws->sorted_weights,
-                              ws->scatter_map));
+                              ws->scatter_map, p->plan));
   return B200MOE_OK;
 }
 
@@ -318,7 +342,8 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   for (int i = 0; i < 9; ++i) segs.start[i] = p->out_seg_start[i];
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
-                              p->output, p->output_f32, segs));
+                              p->output, p->output_f32, segs, p->plan, static_cast<const int*>(ws->status),
+                              ws->status_mirror));
   return B200MOE_OK;
 }
 

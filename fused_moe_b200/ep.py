@@ -11,7 +11,8 @@ The reference is single-GPU: its only hook for sharding is ``local_expert_offset
      ITS experts only), giving one partial row per received token, already weighted and summed over its experts;
   4. combine: fp32 partial rows return to the token's home rank, which adds them and rounds once to bf16.
 
-Collectives go over NCCL (NVLink/NVSwitch); payloads land in local HBM before any kernel reads them.  Two classes share
+Payloads cross NVLink/NVSwitch either as plain peer stores from the pack and reduce kernels or as NCCL collectives;
+either way they land in local HBM before any kernel reads them.  Two classes share
 the protocol: ``ExpertParallelMoE`` does the plumbing with torch ops around injected routing / expert callables, so it
 also runs on CPU ranks (gloo) in the tests with the CPU oracle standing in; ``CudaExpertParallelMoE`` is the B200 shard,
 where ranking, packing, the local experts and the final add are kernels of libb200moe.so.
@@ -139,32 +140,49 @@ class ExpertParallelMoE:
 
 class CudaExpertParallelMoE:
     """One rank's shard on a B200, everything on the device done by libb200moe.so: routing, the stable ranking of
-    (token, destination) pairs and record packing (``b200moe_ep_dispatch``), the local experts reading the received
-    records in place (``kernel_from_records``) and the final add (``b200moe_ep_combine``).  torch.distributed only moves
-    bytes: one all_gather of the G x G record counts (read back to the host, which NCCL needs for the split sizes) and
-    one all_to_all_single per direction."""
+    (token, destination) pairs, record packing, the local experts reading the received records in place and the final
+    add.  Two transports:
 
-    def __init__(self, weights: dict, rank: int, world: int, group=None, transport: str = "auto"):
-        """transport: "peer" — records and partial rows are stored straight into the destination GPU's memory by the
-        pack and reduce kernels (torch symmetric memory supplies the mapped buffers; up to 8 GPUs of one node), with a
-        bounded flag barrier between phases and no payload collective; "nccl" — two all_to_all_single; "auto" — peer
-        when it can be set up, else nccl."""
+    "peer" (default up to 8 GPUs of one node): one slab per rank — flags, count matrix, receive records, returned
+    partial rows — is mapped into every rank (torch symmetric memory, plain peer mappings, no multicast).  A step is
+    route -> rank -> count exchange + barrier -> pack (records stored straight into the destinations' slabs) -> barrier
+    -> the layer on the received records, its last kernel storing each fp32 partial row straight into the home rank's
+    slab -> barrier -> combine.  The counts never reach the host: ``b200moe_ep_exchange_counts`` leaves a plan in device
+    memory that the following kernels read, so a step has NO host synchronisation and no collective call.
+
+    "nccl": the records and the partial rows travel with two ``all_to_all_single``; the counts are all-gathered and read
+    back to the host, which the collective needs for its split sizes.
+
+    Capacity: the slab is sized at the first call for ``T_cap`` tokens per rank — the maximum over the ranks of the
+    batch they bring to that call and of ``max_tokens_per_rank`` — so every rank may later bring any batch up to
+    ``T_cap``; a larger batch raises ValueError on the rank that brings it (create the shard with a larger
+    ``max_tokens_per_rank``).  The device re-checks the exchanged counts against the buffer sizes before anything is
+    stored into a peer (status code 3)."""
+
+    HDR_FLAGS, HDR_COUNTS, HDR_BYTES = 0, 256, 1024
+
+    def __init__(self, weights: dict, rank: int, world: int, group=None, transport: str = "auto",
+                 max_tokens_per_rank: Optional[int] = None):
         if E_GLOBAL % world:
             raise ValueError(f"world size {world} does not divide {E_GLOBAL} experts")
         if transport not in ("auto", "peer", "nccl"):
             raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
         self.weights, self.rank, self.world, self.group = weights, rank, world, group
-        self.transport = "nccl" if (world == 1 or world > 8) else transport
+        # more than 8 ranks span several nodes: collectives only; one rank needs no transport at all, "auto" then takes
+        # the shorter collective-free nccl branch and an explicit "peer" runs the peer protocol on a local slab
+        self.transport = "nccl" if (world > 8 or (world == 1 and transport == "auto")) else transport
+        self.max_tokens_per_rank = max_tokens_per_rank
         self._peer = None          # symmetric-memory state of the peer transport
         self._epoch = 0
         self.e_local = E_GLOBAL // world
         self.local_expert_offset = rank * self.e_local
         self._buf = {}
-        self.last_records = None   # records this rank received in the last call (uint8 [n, 7456])
-        self.last_splits = None    # (send_splits, recv_splits) of the last call
+        self._records = None       # nccl transport: records received in the last call
+        self._splits = None
         self.profile = False       # True: record CUDA events around each phase, read them with phase_times()
         self._events = []
 
+    # ------------------------------------------------------------------ bookkeeping
     def _mark(self, name):
         if self.profile:
             ev = torch.cuda.Event(enable_timing=True)
@@ -179,47 +197,134 @@ class CudaExpertParallelMoE:
             out[name] = a.elapsed_time(b) * 1e3
         return out
 
-    def _peer_setup(self, T: int, device):
-        """Maps one slab per rank into every rank: [flags | receive records | returned partial rows].  Collective."""
+    def read_plan(self):
+        """The device-side plan of the last peer-transport call as a ``_lib.EpPlan`` (synchronises; for tests, tools
+        and statistics — the step itself never reads it on the host)."""
+        from . import _lib
+        if self._peer is None:
+            return None
+        torch.cuda.synchronize()
+        raw = bytes(self._peer["plan"].cpu().numpy().tobytes())
         import ctypes as C
+        return _lib.EpPlan.from_buffer_copy(raw[:C.sizeof(_lib.EpPlan)])
+
+    @property
+    def last_splits(self):
+        """(records sent per destination rank, records received per source rank) of the last call (synchronises)."""
+        if self.transport != "peer" or self._peer is None:
+            return self._splits
+        pl = self.read_plan()
+        m = [[pl.matrix[s_rank * 8 + d] for d in range(self.world)] for s_rank in range(self.world)]
+        return m[self.rank], [m[s_rank][self.rank] for s_rank in range(self.world)]
+
+    @property
+    def last_records(self):
+        """The records this rank received in the last call, uint8 [n, 7456] (synchronises on the peer transport)."""
+        if self.transport != "peer" or self._peer is None:
+            return self._records
+        n = self.read_plan().n_recv
+        return self._peer["recv"][:n]
+
+    # ------------------------------------------------------------------ set-up
+    def _agree(self, value: int, op, device) -> int:
+        t = torch.tensor([value], dtype=torch.int64, device=device)
+        if self.world > 1:
+            dist.all_reduce(t, op=op, group=self.group)
+        return int(t.item())
+
+    def _peer_setup(self, T: int, device):
+        """First call only, collective: agrees on the capacity and on whether every rank can use peer memory, then maps
+        one slab per rank into every rank: [flags | count matrix | receive records | returned partial rows]."""
         import os
         from . import _lib
-        if self._peer is not None and self._peer["T"] >= T:
+        if self._peer is not None:
+            if T > self._peer["T_cap"]:
+                raise ValueError(f"{T} tokens exceed the {self._peer['T_cap']} per rank the expert-parallel buffers were "
+                                 "sized for at the first call; create the shard with max_tokens_per_rank")
             return self._peer
+        T_cap = self._agree(max(T, self.max_tokens_per_rank or 0, 1), dist.ReduceOp.MAX, device)
         # plain peer mappings only: no NVLink multicast object is bound to these buffers
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
-        cap_recv = self.world * T                      # every token of every rank may come here
-        cap_back = T * min(TOP_K, self.world)          # one returned row per (token, destination)
-        off_recv = 256
+        cap_recv = self.world * T_cap                      # every token of every rank may come here
+        cap_back = T_cap * min(TOP_K, self.world)          # one returned row per (token, destination)
+        off_recv = self.HDR_BYTES
         off_back = off_recv + (cap_recv * ROW_BYTES + 255) // 256 * 256
         total = off_back + cap_back * H * 4
-        slab = symm_mem.empty(total, dtype=torch.uint8, device=device)
-        slab[:256].zero_()
-        group = self.group if self.group is not None else dist.group.WORLD
-        hdl = symm_mem.rendezvous(slab, group)
-        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        slab, err, hdl = None, None, None
+        if self.world == 1:
+            slab = torch.empty(total, dtype=torch.uint8, device=device)   # the only "peer" is this rank itself
+            slab[:self.HDR_BYTES].zero_()
+            ptrs = [slab.data_ptr()]
+        else:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                slab = symm_mem.empty(total, dtype=torch.uint8, device=device)
+            except Exception as exc:   # no symmetric memory on this build / device
+                err = exc
+            # every rank takes the same branch: the rendezvous below is collective
+            if self._agree(0 if slab is None else 1, dist.ReduceOp.MIN, device) == 0:
+                raise RuntimeError(f"peer transport unavailable on at least one rank ({err!r})")
+            slab[:self.HDR_BYTES].zero_()
+            group = self.group if self.group is not None else dist.group.WORLD
+            hdl = symm_mem.rendezvous(slab, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
         peers = _lib.EpPeers()
-        peers.world, peers.rank = self.world, self.rank
+        peers.world, peers.rank, peers.cap_recv, peers.cap_back = self.world, self.rank, cap_recv, cap_back
         for r in range(self.world):
-            peers.flags[r] = ptrs[r]
+            peers.flags[r] = ptrs[r] + self.HDR_FLAGS
+            peers.counts[r] = ptrs[r] + self.HDR_COUNTS
             peers.recv_records[r] = ptrs[r] + off_recv
+            peers.back_rows[r] = ptrs[r] + off_back
         status = torch.zeros(4, dtype=torch.int32, device=device)
+        plan = torch.zeros(512, dtype=torch.uint8, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group=self.group)                 # flags are zero everywhere before the first epoch
-        self._peer = dict(T=T, slab=slab, hdl=hdl, ptrs=ptrs, peers=peers, off_recv=off_recv, off_back=off_back,
-                          cap_recv=cap_recv, cap_back=cap_back, status=status)
+        if self.world > 1:
+            dist.barrier(group=self.group)             # flags are zero everywhere before the first epoch
+        self._peer = dict(T_cap=T_cap, slab=slab, hdl=hdl, ptrs=ptrs, peers=peers, off_recv=off_recv, off_back=off_back,
+                          cap_recv=cap_recv, cap_back=cap_back, status=status, plan=plan,
+                          status_host=torch.zeros(4, dtype=torch.int32).pin_memory(),
+                          recv=slab[off_recv:off_recv + cap_recv * ROW_BYTES].view(cap_recv, ROW_BYTES))
+        self._peer["status_np"] = self._peer["status_host"].numpy()
         return self._peer
 
+    def _choose_transport(self, T: int, device):
+        """Settles "auto" at the first call, the same way on every rank."""
+        if self.transport == "nccl" or self._peer is not None:
+            return
+        if self.transport == "peer":
+            self._peer_setup(T, device)
+            return
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+            have = 1
+        except Exception:
+            have = 0
+        if self._agree(have, dist.ReduceOp.MIN, device) == 0:
+            self.transport = "nccl"
+            return
+        try:
+            self._peer_setup(T, device)
+            self.transport = "peer"
+        except RuntimeError:
+            self.transport = "nccl"    # raised on every rank alike (the decision inside _peer_setup is collective)
+
     def check_status(self):
-        """Raises if a bounded peer barrier ran out since the last check (synchronises)."""
+        """Raises if a bounded peer wait ran out or the exchanged counts did not fit since the last check
+        (synchronises)."""
         if self._peer is None:
             return
         st = self._peer["status"].cpu().tolist()
         if st[0] != 0:
             self._peer["status"].zero_()
-            raise RuntimeError(f"expert-parallel barrier timed out: code={st[0]} rank={st[1]} waiting_for={st[2]} "
-                               f"epoch={st[3]}")
+            self._peer["status_np"][:] = 0
+            raise RuntimeError(self._status_text(st))
+
+    @staticmethod
+    def _status_text(st):
+        if st[0] == 3:
+            return (f"expert-parallel counts exceed the buffers: rank={st[1]} receive capacity={st[2]} "
+                    f"return capacity={st[3]} (do all ranks pass batches within the agreed capacity?)")
+        return f"expert-parallel barrier timed out: code={st[0]} rank={st[1]} waiting_for={st[2]} epoch={st[3]}"
 
     def _barrier(self, stream):
         import ctypes as C
@@ -229,22 +334,28 @@ class CudaExpertParallelMoE:
                                                   self._peer["status"].data_ptr(), stream), "b200moe_ep_barrier")
 
     def _buffers(self, T: int, device):
+        """Rank-local buffers, sized once for the capacity (peer transport) or per batch size (nccl)."""
         import ctypes as C
         from . import _lib
-        key = (T, device.index)
+        cap_T = self._peer["T_cap"] if self._peer is not None else T
+        key = (cap_T, device.index)
         b = self._buf.get(key)
         if b is None:
             n = C.c_size_t(0)
-            _lib.check(_lib.load().b200moe_ep_scratch_bytes(T, self.world, C.byref(n)), "b200moe_ep_scratch_bytes")
-            cap = T * min(TOP_K, self.world)
+            _lib.check(_lib.load().b200moe_ep_scratch_bytes(cap_T, self.world, C.byref(n)), "b200moe_ep_scratch_bytes")
+            cap = cap_T * min(TOP_K, self.world)
             b = dict(scratch=torch.empty(max(n.value, 256), dtype=torch.uint8, device=device), scratch_bytes=n.value,
-                     send=torch.empty((max(cap, 1), ROW_BYTES), dtype=torch.uint8, device=device),
                      counts=torch.zeros(self.world, dtype=torch.int32, device=device),
-                     slot_map=torch.empty((max(T, 1), TOP_K), dtype=torch.int32, device=device),
+                     slot_map=torch.empty((max(cap_T, 1), TOP_K), dtype=torch.int32, device=device),
+                     idx=torch.empty((max(cap_T, 1), TOP_K), dtype=torch.int32, device=device),
+                     w=torch.empty((max(cap_T, 1), TOP_K), dtype=torch.float32, device=device),
                      all_counts=torch.empty(self.world * self.world, dtype=torch.int32, device=device))
+            if self._peer is None:
+                b["send"] = torch.empty((max(cap, 1), ROW_BYTES), dtype=torch.uint8, device=device)
             self._buf = {key: b}
         return b
 
+    # ------------------------------------------------------------------ the step
     @torch.no_grad()
     def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor,
                 output: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -256,23 +367,24 @@ class CudaExpertParallelMoE:
         device = hidden_states.device
         if output is None:
             output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        self._choose_transport(T, device)
+        if self.transport == "peer":
+            self._peer_setup(T, device)    # capacity check only after the first call
+            np_status = self._peer["status_np"]
+            if np_status[0] != 0:          # copied at the end of an earlier call: no synchronisation here
+                st = [int(x) for x in np_status]
+                np_status[:] = 0
+                self._peer["status"].zero_()
+                raise RuntimeError(self._status_text(st) + "; the output of that call is invalid")
+        b = self._buffers(T, device)
         self._events = []
         self._mark("start")
-        idx, w = K.route(routing_logits, routing_bias, routed_scaling_factor)
+        idx, w = K.route(routing_logits, routing_bias, routed_scaling_factor, out=(b["idx"], b["w"]))
         self._mark("route")
-        if self.transport in ("auto", "peer"):
-            try:
-                self._peer_setup(T, device)
-                self.transport = "peer"
-            except Exception:
-                if self.transport == "peer":
-                    raise
-                self.transport = "nccl"   # symmetric memory is not available here: fall back to the collective path
-        if self.transport == "peer":
-            return self._forward_peer(idx, w, hidden_states, hidden_states_scale, output, T, device)
-        b = self._buffers(T, device)
         hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
         hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
+        if self.transport == "peer":
+            return self._forward_peer(idx, w, hs, hss, output, T, device, b)
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream(device).cuda_stream
             _lib.check(lib.b200moe_ep_dispatch(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(), T,
@@ -294,7 +406,7 @@ class CudaExpertParallelMoE:
             dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
         else:
             recv = send
-        self.last_records, self.last_splits = recv, (send_splits, recv_splits)
+        self._records, self._splits = recv, (send_splits, recv_splits)
         self._mark("all_to_all_records")
         wts = self.weights
         part = K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
@@ -317,63 +429,47 @@ class CudaExpertParallelMoE:
         self._mark("combine")
         return output
 
-
-    def _forward_peer(self, idx, w, hidden_states, hidden_states_scale, output, T, device):
+    def _forward_peer(self, idx, w, hs, hss, output, T, device, b):
+        """Peer transport: nothing below waits for the device or calls a collective."""
         import ctypes as C
         from . import _lib
         from . import kernel as K
         lib = _lib.load()
         pr = self._peer
-        b = self._buffers(T, device)
-        hs = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
-        hss = hidden_states_scale if hidden_states_scale.is_contiguous() else hidden_states_scale.contiguous()
+        peers = C.byref(pr["peers"])
+        plan = pr["plan"].data_ptr()
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream(device).cuda_stream
             _lib.check(lib.b200moe_ep_rank(idx.data_ptr(), T, self.world, b["scratch"].data_ptr(), b["scratch_bytes"],
                                            b["counts"].data_ptr(), b["slot_map"].data_ptr(), stream),
                        "b200moe_ep_rank")
-            self._mark("dispatch_kernels")
-            dist.all_gather_into_tensor(b["all_counts"], b["counts"], group=self.group)
-            m = b["all_counts"].cpu().view(self.world, self.world).tolist()   # m[s][d] = records s sends to d
-            self._mark("counts_exchange_and_host_read")
-            me = self.rank
-            send_splits, recv_splits = m[me], [m[s_rank][me] for s_rank in range(self.world)]
-            n_send, n_recv = sum(send_splits), sum(recv_splits)
-            self.last_splits = (send_splits, recv_splits)
-            # my segment in rank d's receive buffer starts after the segments of the ranks before me
-            row0 = (C.c_int32 * self.world)(*[sum(m[s_rank][d] for s_rank in range(me)) for d in range(self.world)])
-            _lib.check(lib.b200moe_ep_pack_peers(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(), T,
-                                                 C.byref(pr["peers"]), row0, b["scratch"].data_ptr(),
-                                                 b["scratch_bytes"], stream), "b200moe_ep_pack_peers")
+            self._mark("rank_pairs")
+            self._epoch += 1
+            _lib.check(lib.b200moe_ep_exchange_counts(peers, b["counts"].data_ptr(), self._epoch, plan,
+                                                      pr["status"].data_ptr(), stream), "b200moe_ep_exchange_counts")
+            self._mark("count_exchange")
+            _lib.check(lib.b200moe_ep_pack_peers_planned(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(),
+                                                         T, peers, plan, b["scratch"].data_ptr(), b["scratch_bytes"],
+                                                         stream), "b200moe_ep_pack_peers_planned")
             self._barrier(stream)
             self._mark("records_to_peers")
-            recv = pr["slab"][pr["off_recv"]:pr["off_recv"] + n_recv * ROW_BYTES].view(n_recv, ROW_BYTES)
-            self.last_records = recv
-            # rows received from source s return to s's slab, after the rows s sent to the ranks before me
-            starts, bases, acc = [0], [], 0
-            for s_rank in range(self.world):
-                acc += recv_splits[s_rank]
-                starts.append(acc)
-                bases.append(pr["ptrs"][s_rank] + pr["off_back"] + sum(m[s_rank][:me]) * H * 4)
             wts = self.weights
-            K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
-                                  wts["gemm2_weights_scale"], self.local_expert_offset, out_segments=(starts, bases))
+            K.kernel_from_records(pr["recv"], wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
+                                  wts["gemm2_weights_scale"], self.local_expert_offset, plan=plan)
             self._mark("local_experts_and_rows_to_peers")
             self._barrier(stream)
             self._mark("barrier")
-            if output is None:
-                output = torch.empty((T, H), dtype=torch.bfloat16, device=device)
             if T > 0:
-                if n_send == 0:
-                    output.zero_()
-                else:
-                    back_ptr = pr["ptrs"][me] + pr["off_back"]
-                    _lib.check(lib.b200moe_ep_combine(back_ptr, b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
-                               "b200moe_ep_combine")
+                back_ptr = pr["ptrs"][self.rank] + pr["off_back"]
+                _lib.check(lib.b200moe_ep_combine(back_ptr, b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
+                           "b200moe_ep_combine")
             self._mark("combine")
+            # the status word follows the step to pinned host memory; the next call looks at it before it starts
+            pr["status_host"].copy_(pr["status"], non_blocking=True)
         return output
 
 
-def make_cuda_shard(weights: dict, rank: int, world: int, group=None, transport: str = "auto") -> CudaExpertParallelMoE:
+def make_cuda_shard(weights: dict, rank: int, world: int, group=None, transport: str = "auto",
+                    max_tokens_per_rank: Optional[int] = None) -> CudaExpertParallelMoE:
     """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts)."""
-    return CudaExpertParallelMoE(weights, rank, world, group, transport)
+    return CudaExpertParallelMoE(weights, rank, world, group, transport, max_tokens_per_rank)

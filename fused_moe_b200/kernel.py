@@ -48,9 +48,14 @@ class _Workspace:
 
 @dataclass
 class _DeviceState:
+    """Per-device scratch: ONE buffer, carved per (T, E_local), shared by every call on that device.  One workspace
+    serves one stream at a time: calls issued on different streams of a device must be ordered by the caller."""
+
     buffer: Optional[torch.Tensor] = None
     carved: Dict[Tuple[int, int], _Workspace] = field(default_factory=dict)
     active: Optional[Tuple[int, int]] = None
+    mirror: Optional[torch.Tensor] = None   # pinned host int32[4]: the device copies a non-zero status word here
+    mirror_np: object = None                # numpy view of it (a plain memory read per call)
 
 
 _devices: Dict[int, _DeviceState] = {}
@@ -74,9 +79,27 @@ def workspace_bytes(T: int, E_local: int) -> int:
     return n.value
 
 
+def _raise_if_failed(st: _DeviceState) -> None:
+    """Looks at the host-visible mirror of the device status word (a read of host memory, no synchronisation).  The last
+    kernel of a layer call copies a non-zero status there, so a call whose bounded wait ran out is reported by the next
+    call on that device at the latest (``check_status`` reports it at once, at the price of a synchronisation)."""
+    m = st.mirror_np
+    if m is None or m[0] == 0:
+        return
+    code, block, role, detail = (int(x) for x in m)
+    m[:] = 0
+    st.active = None    # next call clears the device status word and the tile tickets (b200moe_workspace_init)
+    raise RuntimeError(f"an earlier layer call failed on the device: status code={code} block={block} role={role} "
+                       f"detail={detail}; its output is invalid")
+
+
 def _workspace(device: torch.device, T: int, E_local: int, stream_ptr: int) -> _Workspace:
     lib = _lib.load()
     st = _devices.setdefault(device.index, _DeviceState())
+    if st.mirror is None:
+        st.mirror = torch.zeros(4, dtype=torch.int32).pin_memory()
+        st.mirror_np = st.mirror.numpy()
+    _raise_if_failed(st)
     need = workspace_bytes(T, E_local)
     if st.buffer is None or st.buffer.numel() < need:
         st.buffer = torch.empty(need, dtype=torch.uint8, device=device)
@@ -89,10 +112,13 @@ def _workspace(device: torch.device, T: int, E_local: int, stream_ptr: int) -> _
         base = st.buffer.data_ptr()
         _lib.check(lib.b200moe_workspace_carve(base, st.buffer.numel(), T, E_local, C.byref(s)),
                    "b200moe_workspace_carve")
+        # pinned host memory is addressable from the device at the same address (unified addressing)
+        s.status_mirror = st.mirror.data_ptr()
         ws = _Workspace(struct=s, base_ptr=base, buffer=st.buffer)
         st.carved[key] = ws
     if st.active != key:
-        # the status word sits at a (T, E_local)-dependent offset of the shared buffer
+        # the status word and the tile tickets sit at (T, E_local)-dependent offsets of the shared buffer: clear them
+        # when the layout changes (and after a failed call, which may have left tickets behind)
         _lib.check(lib.b200moe_workspace_init(C.byref(ws.struct), stream_ptr), "b200moe_workspace_init")
         st.active = key
     return ws
@@ -364,12 +390,15 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
 
 @torch.no_grad()
 def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
-                        local_expert_offset, output=None, out_segments=None):
+                        local_expert_offset, output=None, out_segments=None, plan=None):
     """The layer over expert-parallel dispatch records read in place: ``records`` is uint8 [n, 7456] in the layout of
     ``b200moe_ep_dispatch`` (activations | 56 scales | 8 expert ids | 8 weights per row).  Returns float32 [n, 7168]
     partial rows (sum over THIS shard's experts), in record order.  With ``out_segments = (starts, bases)`` — row
     ranges ``starts[i]..starts[i+1]`` and raw float32 device addresses ``bases[i]`` (at most 8, possibly peer-GPU
-    memory) — the rows are stored there instead and nothing is returned.  No reference counterpart."""
+    memory) — the rows are stored there instead and nothing is returned.  With ``plan`` (device address of a
+    ``b200moe_ep_plan`` filled by ``b200moe_ep_exchange_counts``) ``records`` is the whole receive buffer (its row
+    count is a capacity): how many leading rows are real and where their partial rows go is read on the device, so the
+    host never learns the count; nothing is returned.  No reference counterpart."""
     if not torch.is_tensor(records) or records.dim() != 2 or records.shape[1] != _lib.EP_RECORD_BYTES:
         raise ValueError(f"records must be uint8 [n, {_lib.EP_RECORD_BYTES}]")
     if records.dtype != torch.uint8 or not records.is_contiguous():
@@ -383,7 +412,10 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
     if offset < 0 or offset + E_local > E_GLOBAL:
         raise ValueError(f"local_expert_offset {offset} with {E_local} local experts exceeds {E_GLOBAL} experts")
     device = records.device
-    if out_segments is not None:
+    if plan is not None:
+        if out_segments is not None or output is not None:
+            raise ValueError("plan excludes output and out_segments")
+    elif out_segments is not None:
         starts, bases = out_segments
         if len(bases) > 8 or len(starts) != len(bases) + 1 or starts[0] != 0 or starts[-1] != n:
             raise ValueError("out_segments must cover rows 0..n with at most 8 segments")
@@ -403,7 +435,9 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
         p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
         p.gemm1_weights, p.gemm1_weights_scale = w13.data_ptr(), w13s.data_ptr()
         p.gemm2_weights, p.gemm2_weights_scale = w2.data_ptr(), w2s.data_ptr()
-        if out_segments is None:
+        if plan is not None:
+            p.output, p.output_f32, p.plan = None, None, int(plan)
+        elif out_segments is None:
             p.output, p.output_f32 = None, output.data_ptr()
         else:
             p.output, p.output_f32 = None, None
@@ -417,10 +451,11 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
 
 
 @torch.no_grad()
-def route(routing_logits, routing_bias, routed_scaling_factor):
+def route(routing_logits, routing_bias, routed_scaling_factor, out=None):
     """Routing stage alone -> (topk_idx int32 [T,8], topk_weights float32 [T,8]); experts in descending biased score,
     ties to the lower id (reference: solution/python/pure_triton_impl.py:96-190).  Used by expert-parallel ranks, which
-    route their own tokens before dispatch."""
+    route their own tokens before dispatch.  ``out`` = (idx, w) tensors to fill (their first T rows); needs no
+    workspace (``b200moe_route_topk``)."""
     if not torch.is_tensor(routing_logits) or routing_logits.dim() != 2:
         raise ValueError("routing_logits must be [T, 256]")
     T = int(routing_logits.shape[0])
@@ -428,18 +463,24 @@ def route(routing_logits, routing_bias, routed_scaling_factor):
     bias = _require(routing_bias.reshape(-1), "routing_bias", torch.bfloat16, (E_GLOBAL,))
     _require_cuda(routing_logits=logits, routing_bias=bias)
     device = logits.device
+    if out is None:
+        idx = torch.empty((T, TOP_K), dtype=torch.int32, device=device)
+        w = torch.empty((T, TOP_K), dtype=torch.float32, device=device)
+    else:
+        idx, w = out
+        if (idx.dtype != torch.int32 or w.dtype != torch.float32 or idx.shape[0] < T or w.shape[0] < T
+                or tuple(idx.shape[1:]) != (TOP_K,) or tuple(w.shape[1:]) != (TOP_K,) or not idx.is_contiguous()
+                or not w.is_contiguous() or idx.device != device or w.device != device):
+            raise ValueError("out must be (int32 [>=T,8], float32 [>=T,8]) contiguous tensors on the logits' device")
+        idx, w = idx[:T], w[:T]
     if T == 0:
-        return (torch.empty((0, TOP_K), dtype=torch.int32, device=device),
-                torch.empty((0, TOP_K), dtype=torch.float32, device=device))
+        return idx, w
     with torch.cuda.device(device):
-        stream_ptr = torch.cuda.current_stream(device).cuda_stream
-        ws = _workspace(device, T, 1, stream_ptr)
-        p = _lib.Problem()
-        p.T, p.E_local, p.local_expert_offset = T, 1, 0
-        p.routed_scaling_factor = _host_scalar(routed_scaling_factor, float)
-        p.routing_logits, p.routing_bias = logits.data_ptr(), bias.data_ptr()
-        _lib.check(_lib.load().b200moe_route(C.byref(p), C.byref(ws.struct), stream_ptr), "b200moe_route")
-        return ws.view("topk_idx", torch.int32, (T, TOP_K)).clone(), ws.view("topk_w", torch.float32, (T, TOP_K)).clone()
+        _lib.check(_lib.load().b200moe_route_topk(logits.data_ptr(), bias.data_ptr(), T,
+                                                  _host_scalar(routed_scaling_factor, float), idx.data_ptr(),
+                                                  w.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                   "b200moe_route_topk")
+    return idx, w
 
 
 def check_status(device=None) -> None:
@@ -455,6 +496,9 @@ def check_status(device=None) -> None:
         rc = _lib.load().b200moe_read_status(C.byref(ws.struct), torch.cuda.current_stream(device).cuda_stream,
                                              C.byref(out))
     if rc == _lib.EDEVICE:
+        st.active = None      # the next call re-runs b200moe_workspace_init: tile tickets may not be back at zero
+        if st.mirror is not None:
+            st.mirror.zero_()
         raise RuntimeError(f"device status word: code={out[0]} block={out[1]} role={out[2]} detail={out[3]}")
     _lib.check(rc, "b200moe_read_status")
 

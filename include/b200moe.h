@@ -73,6 +73,7 @@ enum {
  * ids and [T,8] float32 final weights — are used instead.  This is the path the expert-parallel receiver takes for
  * tokens routed on another rank; the reference has no counterpart (it only has `local_expert_offset`,
  * solution/python/pure_triton_impl.py:2141). */
+struct b200moe_ep_plan;
 typedef struct b200moe_problem {
   int32_t T;
   int32_t E_local;
@@ -103,6 +104,13 @@ typedef struct b200moe_problem {
   int32_t out_seg_count;
   int32_t out_seg_start[9];
   float* out_seg_base[8];
+  /* Optional DEVICE pointer (expert-parallel receiver, see b200moe_ep_exchange_counts): when set, the number of valid
+   * rows and the placement of the float32 result rows are read on the device from *plan instead of from the host —
+   * only the first plan->n_recv of the T rows exist (T is then a capacity: the rest is skipped by every stage), and row
+   * r of segment s goes to plan->seg_base[s] + (r - plan->seg_start[s]) * 7168.  `output`, `output_f32` and out_seg_*
+   * are ignored.  This is what lets a rank launch the layer on received records without reading their count back to
+   * the host. */
+  const struct b200moe_ep_plan* plan;
 } b200moe_problem;
 
 /* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
@@ -137,6 +145,10 @@ typedef struct b200moe_workspace {
   int32_t* gemm_tile_ctr;    /* [(R_max / 64) * 28] tickets of GEMM tiles shared by several CTAs; zero between launches
                                 (b200moe_workspace_init clears it, the kernels return it to zero) */
   float* gemm_partial;       /* [B200MOE_GEMM_MAX_CTAS, 2, 2 * 64 * 128] float32 partial sums of shared tiles */
+  int32_t* status_mirror;    /* optional, set by the caller after carving (carve leaves it NULL): device-accessible
+                                address of 4 ints in MAPPED HOST memory.  The last kernel of b200moe_forward copies a
+                                non-zero status word there, so the host can notice a failed call by reading its own
+                                memory, without synchronising the stream.  Never written while status is 0. */
 } b200moe_workspace;
 
 /* Library / build identification.  No reference counterpart. */
@@ -175,6 +187,10 @@ int b200moe_quantize_act(const void* x_bf16, int32_t T, void* q_out, float* scal
  * normalise, scale; also records which local experts each 32-token chunk selected (chunk_bits).
  * Replaces triton_ds_routing_kernel / _fused_routing_histogram_kernel (solution/python/pure_triton_impl.py:96-265). */
 int b200moe_route(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* The same routing into caller-owned arrays topk_idx / topk_w [T,8], without a workspace and without the selection
+ * bits: an expert-parallel rank routes its own tokens this way before dispatch.  Same reference kernels as above. */
+int b200moe_route_topk(const float* routing_logits, const uint16_t* routing_bias, int32_t T,
+                       float routed_scaling_factor, int32_t* topk_idx, float* topk_w, void* stream);
 /* chunk_bits from an existing topk_idx (used when routing ran elsewhere).  No reference counterpart. */
 int b200moe_topk_bits(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
 /* Per-expert prefix over chunks (chunk_base, counts), then the padded layout and the stable scatter
@@ -265,7 +281,27 @@ typedef struct b200moe_ep_peers {
   int32_t rank;
   uint8_t* recv_records[8];
   int32_t* flags[8];
+  /* used by b200moe_ep_exchange_counts only (may stay NULL / 0 otherwise): */
+  int32_t* counts[8];    /* rank r's copy of the count matrix, int32 [8][8]: counts[r][s*8+d] = records s sends to d */
+  float* back_rows[8];   /* rank r's buffer for the float32 partial rows returning to it, [cap_back, 7168] */
+  int32_t cap_recv;      /* records every receive buffer holds */
+  int32_t cap_back;      /* rows every return buffer holds */
 } b200moe_ep_peers;
+/* What one rank needs to know about a step's traffic, computed ON THE DEVICE by b200moe_ep_exchange_counts and read
+ * there by the kernels that follow (pack, the layer on the received records, the return of partial rows), so that no
+ * count ever travels to the host.  ok = 0 (and every count 0) if a barrier wait ran out or the counts would overflow a
+ * buffer; the status word then holds code 2 or 3. */
+typedef struct b200moe_ep_plan {
+  int32_t ok;
+  int32_t n_recv;        /* records this rank receives = valid leading rows of its receive buffer */
+  int32_t n_send;        /* records this rank sends */
+  int32_t seg_count;     /* = world */
+  int32_t seg_start[9];  /* received rows [seg_start[s], seg_start[s+1]) come from rank s */
+  int32_t dst_row0[8];   /* this rank's records for rank d start at row dst_row0[d] of d's receive buffer */
+  int32_t reserved;
+  float* seg_base[8];    /* where the partial rows of segment s go: inside rank s's return buffer */
+  int32_t matrix[64];    /* the count matrix, matrix[s*8+d] */
+} b200moe_ep_plan;
 int b200moe_ep_rank(const int32_t* topk_idx, int32_t T, int32_t world, void* scratch, size_t scratch_bytes,
                     int32_t* send_counts, int32_t* slot_map, void* stream);
 int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
@@ -273,6 +309,20 @@ int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const ui
                           const int32_t* dst_row0 /* host, [world] */, void* scratch, size_t scratch_bytes,
                           void* stream);
 int b200moe_ep_barrier(const b200moe_ep_peers* peers /* host */, int32_t epoch, int32_t* status, void* stream);
+/* Count exchange without the host: every rank stores its `send_counts[world]` (device, from b200moe_ep_rank) into row
+ * `rank` of every peer's count matrix, passes the same bounded flag barrier as b200moe_ep_barrier, and then derives
+ * *plan (device memory of this rank) from its own, now complete, copy of the matrix.  Replaces an all-gather of the
+ * counts plus a device-to-host read.  b200moe_ep_pack_peers_planned is b200moe_ep_pack_peers with the destination rows
+ * taken from the plan on the device; b200moe_forward with b200moe_problem.plan set is the receiver. */
+int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers /* host */, const int32_t* send_counts, int32_t epoch,
+                               b200moe_ep_plan* plan, int32_t* status, void* stream);
+int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
+                                  const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers /* host */,
+                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, void* stream);
+/* Upper bound, in SM clock cycles, of the waits inside b200moe_ep_barrier and b200moe_ep_exchange_counts for launches
+ * made after this call (process-wide; 0 restores the default of about 2 s).  Tests use it to make a wait run out
+ * quickly; a deployment can use it to bound how long a lost peer stalls a step. */
+int b200moe_set_wait_limit_cycles(int64_t cycles);
 int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output, void* stream);
 
 /* Synchronises `stream`, copies the device status word to *status (host) and clears it.

@@ -65,7 +65,8 @@ def test_workspace_sizing_and_carving(lib):
     assert lib.b200moe_workspace_carve(base, need, 7, 4, C.byref(ws)) == 0
     assert (ws.T, ws.E_local, ws.n_chunks) == (7, 4, 1)
     assert ws.R_max == (8 * 7 // 128 + 4) * 128
-    ptrs = [getattr(ws, f[0]) for f in _lib.Workspace._fields_[4:]]
+    assert _lib.Workspace._fields_[-1][0] == "status_mirror" and not ws.status_mirror   # the caller's to set
+    ptrs = [getattr(ws, f[0]) for f in _lib.Workspace._fields_[4:-1]]
     assert ptrs == sorted(ptrs) and all(p % 256 == 0 for p in ptrs)
     assert ptrs[0] == base and ptrs[-1] + 2 * ws.R_max * 7168 <= base + need
     assert lib.b200moe_workspace_carve(base, need - 1, 7, 4, C.byref(ws)) == _lib.EWORKSPACE

@@ -294,13 +294,8 @@ def test_empty_batch(moe):
     assert out.shape == (0, 7168)
 
 
-def test_expert_parallel_shard_world1(moe):
-    """The expert-parallel plumbing with one rank (dispatch and combine are local copies) reproduces kernel()."""
-    from fused_moe_b200 import ep
-    inp = gpu_inputs(300, 32, 4, 64, True)
-    want = moe.kernel(**inp).clone()
-    full = dict(inp)
-    # a world-1 shard owns all 256 experts: embed the 32 generated experts at their global position
+def _world1_weights(inp):
+    """A world-1 shard owns all 256 experts: the 32 generated experts at their global position, zeros elsewhere."""
     E = 256
     w13 = torch.zeros((E, 4096, 7168), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
     w13s = torch.zeros((E, 32, 56), dtype=torch.float32, device="cuda")
@@ -308,13 +303,39 @@ def test_expert_parallel_shard_world1(moe):
     w2s = torch.zeros((E, 56, 16), dtype=torch.float32, device="cuda")
     w13[64:96], w13s[64:96], w2[64:96], w2s[64:96] = (inp["gemm1_weights"], inp["gemm1_weights_scale"],
                                                       inp["gemm2_weights"], inp["gemm2_weights_scale"])
-    shard = ep.make_cuda_shard(dict(gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2,
-                                    gemm2_weights_scale=w2s), rank=0, world=1)
-    got = shard.forward(inp["routing_logits"], inp["routing_bias"], inp["hidden_states"], inp["hidden_states_scale"],
-                        inp["routed_scaling_factor"])
-    moe.check_status()
-    # experts outside 64..95 have zero weights and add nothing: same sums, same single rounding
-    assert torch.equal(got, want)
+    return dict(gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2, gemm2_weights_scale=w2s)
+
+
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+def test_expert_parallel_shard_world1(moe, transport):
+    """The expert-parallel plumbing with one rank reproduces kernel() bit for bit.  "nccl": dispatch and combine are
+    local copies.  "peer": the whole device-side protocol on a local slab — count exchange and plan on the device,
+    records packed into the receive buffer, the layer over a receive buffer LARGER than what arrived (capacity 512
+    tokens; the rows beyond the count are poisoned and, on the later calls, hold the previous call's records), partial
+    rows placed through the plan, combine.  Three calls with different batches share the buffers."""
+    from fused_moe_b200 import ep, synth
+    inp = gpu_inputs(300, 32, 4, 64, True)
+    shard = ep.make_cuda_shard(_world1_weights(inp), rank=0, world=1, transport=transport, max_tokens_per_rank=512)
+    for T, seed in ((300, 4), (77, 11), (412, 12)):
+        cur = synth.make_inputs(T, 32, seed=seed, local_expert_offset=64, skew=(seed != 11), device="cuda", weights=inp)
+        want = moe.kernel(**cur).clone()
+        if transport == "peer" and shard._peer is not None:
+            shard._peer["recv"][T:].fill_(0xFF)     # stale / poisoned rows past the received count must select nothing
+        got = shard.forward(cur["routing_logits"], cur["routing_bias"], cur["hidden_states"],
+                            cur["hidden_states_scale"], cur["routed_scaling_factor"])
+        moe.check_status()
+        shard.check_status()
+        # experts outside 64..95 have zero weights and add nothing: same sums, same single rounding
+        assert torch.equal(got, want), f"T={T}"
+        send, recv = shard.last_splits
+        assert send == [T] and recv == [T] and shard.last_records.shape == (T, 7456)
+    if transport == "peer":
+        pl = shard.read_plan()
+        assert pl.ok == 1 and pl.n_recv == 412 and pl.n_send == 412 and pl.seg_start[1] == 412 and pl.dst_row0[0] == 0
+        with pytest.raises(ValueError):             # beyond the capacity agreed at the first call
+            big = synth.make_inputs(513, 32, seed=1, local_expert_offset=64, device="cuda", weights=inp)
+            shard.forward(big["routing_logits"], big["routing_bias"], big["hidden_states"], big["hidden_states_scale"],
+                          big["routed_scaling_factor"])
 
 
 def test_synth_cpu_and_cuda_generate_identical_bytes(moe):

@@ -65,8 +65,12 @@ def test_sort_static_matches_sort_twice_in_a_row():
         pytest.skip("no CUDA device")
     from fused_moe_b200 import _lib, kernel as K, synth
     lib = _lib.load()
-    # second call: fewer tokens, more experts, another offset — it reuses the array the first call filled
-    for T, E, off, seed, skew in ((300, 32, 64, 4, True), (77, 64, 128, 9, False)):
+    # second call: fewer tokens, more experts, another offset — it reuses the array the first call filled.  The third
+    # and fourth have more than 32 chunks of 32 tokens, where the sort uses BOTH tables of the fixed array (the bit
+    # matrix and the per-chunk prefix) and a separate scan kernel; they run right after a smaller call, and the last is
+    # smaller again, so leftovers of every size are in the array at some point.
+    for T, E, off, seed, skew in ((300, 32, 64, 4, True), (77, 64, 128, 9, False), (1100, 8, 16, 2, True),
+                                  (2000, 16, 208, 6, False), (33, 256, 0, 7, True)):
         inp = synth.make_inputs(T, E, seed=seed, local_expert_offset=off, skew=skew, device="cuda", only_experts=[])
         idx, w = K.route(inp["routing_logits"], inp["routing_bias"], 2.5)
         want = _sorted_reference(lib, K, idx, w, T, E, off)
