@@ -28,7 +28,7 @@ def lib():
 
 def _layer_still_correct(oracle, seed):
     from fused_moe_b200 import kernel as K, synth
-    inp = synth.make_inputs(40, 4, seed=seed, local_expert_offset=96, skew=True, device="cuda")
+    inp = synth.make_inputs(40, 8, seed=seed, local_expert_offset=96, skew=True, device="cuda")
     out = K.kernel(**inp)
     K.check_status()
     ref = oracle.kernel(*[inp[k] for k in KEYS])
@@ -99,7 +99,7 @@ def test_failed_call_is_reported_by_the_next_call_without_a_sync(oracle):
     last kernel of every layer call copies a non-zero status into pinned host memory, which kernel() looks at on entry.
     The failure is staged by writing the status word from the host (no kernel is made to fail)."""
     from fused_moe_b200 import kernel as K, synth
-    inp = synth.make_inputs(40, 4, seed=8, local_expert_offset=96, skew=True, device="cuda")
+    inp = synth.make_inputs(40, 8, seed=8, local_expert_offset=96, skew=True, device="cuda")
     good = K.kernel(**inp).clone()
     K.check_status()
     ws = K.last_workspace()
@@ -111,4 +111,4 @@ def test_failed_call_is_reported_by_the_next_call_without_a_sync(oracle):
     out = K.kernel(**inp)                # the workspace is re-initialised: the library works again
     K.check_status()
     assert torch.equal(out, good)
-    _layer_still_correct(oracle, seed=5)
+    _layer_still_correct(oracle, seed=8)
