@@ -46,8 +46,34 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival that orders nothing: for hand-backs where no memory written by this thread is read by the waiter (a TMEM stage
+// whose columns are already in registers: tcgen05.wait::ld + tcgen05.fence::before_thread_sync).  The default arrival
+// has release semantics, and a release waits for the thread's memory operations in flight: with the next chunk's scale
+// loads under way it reached the barrier ~600 cycles after the warp had finished reading TMEM (cycle stamps), which held
+// the tensor pipe at ~50 % duty.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// One poll of a barrier phase.  The instruction may park the thread in hardware until the phase completes or
+// B200MOE_WAIT_HINT_NS nanoseconds have passed, whichever comes first; completion wakes it at once.  Parked threads issue
+// nothing, which matters here: the single-thread roles (TMA producer, MMA issuer) share their SM sub-partitions with the
+// promotion warps, and a role that re-issued a failing poll every few cycles took enough issue slots to make the
+// promotion warps on its sub-partition ~500 cycles late per 128-K chunk (cycle stamps: the warp next to the producer
+// saw a completed barrier 850 cycles after the MMA issue, a warp on a quiet sub-partition after 350).
+#ifndef B200MOE_WAIT_HINT_NS
+#define B200MOE_WAIT_HINT_NS 20000
+#endif
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if B200MOE_WAIT_HINT_NS > 0
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(B200MOE_WAIT_HINT_NS))
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -55,20 +81,29 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok;
 }
 // Wait on an mbarrier phase with a time limit.  Returns false (and records why) instead of hanging: `abort_flag` is a
-// CTA-shared word every waiting role polls, so one role giving up releases the others quickly.  The limit is counted
-// on the SM's cycle counter, read only once per 1024 polls, so a healthy wait (microseconds) never touches a timer.
+// CTA-shared word every waiting role looks at between polls, so one role giving up releases the others within one poll
+// period.  The limit is counted on the SM's cycle counter, read only when a poll came back empty, so a healthy wait
+// (microseconds) costs one instruction.
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s at B200 clocks
+// polls a giving-up role spends on each of its copies still in flight (each poll may take up to the hint)
+constexpr int DRAIN_POLLS = B200MOE_WAIT_HINT_NS > 0 ? (1 << 14) : (1 << 20);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int role, int detail) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
+#if B200MOE_WAIT_HINT_NS > 0
+  constexpr uint32_t CHECK_MASK = 0x0;     // a failed poll already took up to the hint: check every time
+#else
+  constexpr uint32_t CHECK_MASK = 0x3ff;   // polls return at once: look at the clock every 1024 tries
+#endif
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & CHECK_MASK) == 0) {
       if (*abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;
@@ -205,71 +240,6 @@ template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 
-// ---------------------------------------------------------------------------------------------------------
-// CTA pairs (cta_group::2): two CTAs of one cluster drive one 256-row MMA, each holding its half of B.
-// No TMA multicast is involved: every CTA loads its own operands; only barrier SIGNALS cross the pair.
-// ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-// Arrival on a barrier of another CTA of the cluster.  Default semantics (release at CTA scope): the cluster-scope
-// release form measured ~320 cycles per arrival on B200 (and ~840 with memory operations in flight), which is what made
-// a per-chunk hand-back across a CTA pair slow; this form retires in a few cycles.  The data handed back (TMEM columns
-// already read into registers, tcgen05.wait::ld + tcgen05.fence::before_thread_sync) needs no memory ordering.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// TMA load issued by either CTA of a pair; the transaction bytes are counted on the barrier at `leader_bar`
-// (a shared::cluster address in the pair's even CTA).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, uint32_t leader_bar, int c0,
-                                                 int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
-      "[%2];" ::"r"(smem_dst),
-      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(leader_bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// The barrier at the same shared-memory offset in every CTA named by `cta_mask` gets one arrival once every MMA issued
-// so far by this thread has completed (a signal fan-out, not a data multicast).
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-      "h"(cta_mask)
-      : "memory");
-}
-// D[tmem of both CTAs] (+)= A[256 rows, 128 per CTA] * B[N, N/2 rows per CTA]; issued by ONE thread of the even CTA.
-__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // UMMA shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle
 // (8-row x 128-byte atoms, 1024 bytes apart).  Bits: [0,14) address>>4, [16,30) leading byte offset>>4 (unused for
 // swizzled K-major, set to 1), [32,46) stride byte offset>>4 (= 1024>>4), [46,48) version 1, [61,64) layout 2.
@@ -312,27 +282,6 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
-// Same, as clusters of `cluster_x` CTAs (grid.x must be a multiple of it).
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                      unsigned cluster_x, Args&&... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = cluster_x;
-  attr[1].val.clusterDim.y = 1;
-  attr[1].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

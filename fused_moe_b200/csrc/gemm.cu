@@ -15,15 +15,16 @@
 // row.  MODE 1 uses two 128-row weight boxes per chunk (W1 rows n0.., W3 rows 2048+n0..) laid out back to back so a
 // single N=256 MMA produces both SwiGLU operands; MODE 2 uses one 256-row box of W2 and two A boxes (the two terms).
 //
-// The kernel is written for CG = 1 (one CTA per tile, shipped) and CG = 2 (CTA pairs, compile with
-// -DB200MOE_CTA_GROUP=2).  With one CTA per tile the tensor core's operand reads (96 B/clk) plus the TMA writes
-// (96 B/clk) exceed what shared memory delivers, and a 128-K chunk takes ~770 cycles instead of 512 (cycle-stamp
-// traces).  CTA pairs fix that on paper: two CTAs of a cluster work on one 256-row x 256-column tile with
-// `tcgen05.mma.cta_group::2`, each loading its own 128 rows of A and its own HALF of the weight tile (32 KB per chunk
-// instead of 48; nothing multicast, only barrier signals cross the pair).  Measured, the pair version is correct but
-// 2x SLOWER (T=16384, 32 experts: GEMM1 940 us vs 469 us): the per-chunk promotion hand-shake then crosses SMs twice
-// per chunk (MMA completion fan-out to the partner, TMEM hand-back from the partner) and with only two TMEM stages that
-// latency cannot be hidden.  It stays in the source as a measured alternative, not as a second product path.
+// One CTA per tile.  What paces it (cycle stamps, probes): a TMEM stage goes round MMA -> completion signal -> promotion
+// warps read it (two 64-column loads per warp) -> hand-back -> next MMA into it, and with 512 TMEM columns there are
+// only two such stages of 256 columns.  A round costs ~600 cycles of tensor work (four MMAs of 128 cycles plus issue
+// gaps) and ~1100-1300 cycles of latencies (barrier wake-ups of 190-280 cycles each way, 260 for the two loads, 150 to
+// the hand-back, 170 to re-check the operands), so two stages keep the tensor pipe ~55 % busy: ~970 cycles per 128-K
+// chunk.  Things that were built, measured and did NOT move it: CTA pairs (tcgen05.mma.cta_group::2, each CTA loading
+// half of the weight tile: fewer L2 bytes, but the hand-back then crosses SMs; 485 vs 456 us, also 7 % of pair padding),
+// a second MMA-issuing thread (one per TMEM stage), parking barrier polls with a suspend-time hint, and a relaxed
+// instead of a releasing hand-back arrival.  In isolation the pieces run at 512 (MMA), 320 (promotion, 8 warps) and
+// 610-690 (48 KB of loads per SM from L2, all SMs) cycles per chunk, and ~600 when all three run unsynchronised.
 //
 // Warp roles (384 threads): warps 0-7 promote TMEM partials into fp32 registers and run the epilogue (warp w owns TMEM
 // lanes 32*(w%4).. and half of the columns), warp 8 issues TMA loads, warp 9 owns TMEM and issues the MMAs, warps 10-11
@@ -47,17 +48,13 @@ constexpr int NUM_PROMO_WARPS = 8;
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
 constexpr int GEMM_THREADS = 384;            // 3 warpgroups: 2 x promotion, 1 x {TMA, MMA, 2 idle warps}
-#ifndef B200MOE_CTA_GROUP
-#define B200MOE_CTA_GROUP 1
-#endif
-constexpr int CTA_GROUP = B200MOE_CTA_GROUP;  // CTAs per tile: 1 = single CTA (shipped), 2 = CTA pairs (see above)
 
-template <int MODE, int CG>
+template <int MODE>
 struct Cfg {
   static constexpr int A_TILES = (MODE == 1) ? 1 : 2;
-  static constexpr int B_BYTES = (TILE_N / CG) * 128;  // this CTA's share of the 256-row weight tile
+  static constexpr int B_BYTES = TILE_N * 128;         // the 256-row weight tile of one chunk
   static constexpr int STAGE_BYTES = A_TILES * A_TILE_BYTES + B_BYTES;
-  static constexpr int STAGES = (196608 / STAGE_BYTES) > 6 ? 6 : (196608 / STAGE_BYTES);  // 4/3 (CG 1), 6/4 (CG 2)
+  static constexpr int STAGES = 196608 / STAGE_BYTES;  // 4 (GEMM1, 48 KB), 3 (GEMM2, 64 KB)
   static constexpr int K_CHUNKS = (MODE == 1) ? H_BLOCKS : I_BLOCKS;
   static constexpr int N_TILES = (MODE == 1) ? (I / 128) : (H / 256);  // 16, 28
 };
@@ -66,37 +63,34 @@ struct TileInfo {
   int e, nt, mblk, m_local, cnt;
 };
 
-// Tiles are numbered expert-major, then n-tile, then row group (a row group = CG consecutive 128-row blocks of one
-// expert), so CTAs that run at the same time share weight tiles in L2.  s_grp[e] = row groups before expert e.
-template <int CG>
-__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_grp, const int* s_off, const int* s_cnt, int E,
-                                                int NT, int cta_rank) {
+// Tiles are numbered expert-major, then n-tile, then 128-row block, so CTAs that run at the same time share weight
+// tiles in L2.  s_off[e] = row blocks before expert e (block_offsets).
+__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_off, const int* s_cnt, int E, int NT) {
   int lo = 0, hi = E - 1;
   while (lo < hi) {
     int mid = (lo + hi + 1) >> 1;
-    if (s_grp[mid] * NT <= tile) lo = mid; else hi = mid - 1;
+    if (s_off[mid] * NT <= tile) lo = mid; else hi = mid - 1;
   }
   TileInfo ti;
   ti.e = lo;
-  int local = tile - s_grp[lo] * NT;
-  int groups = s_grp[lo + 1] - s_grp[lo];
+  int local = tile - s_off[lo] * NT;
+  int groups = s_off[lo + 1] - s_off[lo];
   ti.nt = local / groups;
-  ti.m_local = (local - ti.nt * groups) * CG + cta_rank;  // may be one past the expert's last block in the odd CTA
+  ti.m_local = local - ti.nt * groups;
   ti.mblk = s_off[lo] + ti.m_local;
   ti.cnt = s_cnt[lo];
   return ti;
 }
 
 struct __align__(8) GemmAux {
-  uint64_t full[6];
-  uint64_t empty[6];
+  uint64_t full[4];
+  uint64_t empty[4];
   uint64_t tfull[2];
   uint64_t tempty[2];
   uint64_t xbar[2];
   uint32_t tmem_base;
   int abort_flag;
   int off[E_GLOBAL + 1];
-  int grp[E_GLOBAL + 1];
   int cnt[E_GLOBAL];
   float amax[2][2][BLOCK_M];
   // GEMM2 epilogue: per promotion warp, 32 rows x 16 columns (+4 padding: conflict-free 16-byte accesses) through which
@@ -104,15 +98,15 @@ struct __align__(8) GemmAux {
   float out_stage[NUM_PROMO_WARPS][32][20];
 };
 
-template <int MODE, int CG>
+template <int MODE>
 constexpr size_t gemm_smem_bytes() {
-  return 1024 + static_cast<size_t>(Cfg<MODE, CG>::STAGES) * Cfg<MODE, CG>::STAGE_BYTES + sizeof(GemmAux);
+  return 1024 + static_cast<size_t>(Cfg<MODE>::STAGES) * Cfg<MODE>::STAGE_BYTES + sizeof(GemmAux);
 }
 
-template <int MODE, int CG>
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs args) {
-  using C = Cfg<MODE, CG>;
+  using C = Cfg<MODE>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
@@ -123,10 +117,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int E = args.E_local;
   constexpr int NT = C::N_TILES;
-  const int cta_rank = (CG == 2) ? static_cast<int>(cluster_ctarank()) : 0;
-  const bool leader = cta_rank == 0;          // the even CTA of a pair issues the MMAs and owns the shared barriers
-  const int group_id = blockIdx.x / CG;       // tiles are dealt to CTA groups
-  const int num_groups = gridDim.x / CG;
+  const int group_id = blockIdx.x;            // tiles are dealt round-robin to the CTAs
+  const int num_groups = gridDim.x;
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) aux->abort_flag = 0;
@@ -138,7 +130,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&aux->tfull[a]), 1);
-      mbar_init(smem_u32(&aux->tempty[a]), NUM_PROMO_WARPS * CG);
+      mbar_init(smem_u32(&aux->tempty[a]), NUM_PROMO_WARPS);
       mbar_init(smem_u32(&aux->xbar[a]), NUM_PROMO_WARPS);
     }
     fence_mbar_init();
@@ -146,46 +138,20 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tma_prefetch_desc(&tmB);
   }
   if (warp == MMA_WARP) {
-    if (CG == 2) { tmem_alloc_pair(smem_u32(&aux->tmem_base), 512); tmem_relinquish_pair(); }
-    else { tmem_alloc(smem_u32(&aux->tmem_base), 512); tmem_relinquish(); }
+    tmem_alloc(smem_u32(&aux->tmem_base), 512);
+    tmem_relinquish();
   }
   // everything above is CTA-local set-up and may overlap the tail of the previous kernel; the layout it wrote is
   // read only from here on
   pdl_wait();
   for (int i = threadIdx.x; i <= E; i += GEMM_THREADS) aux->off[i] = __ldg(args.block_offsets + i);
   for (int i = threadIdx.x; i < E; i += GEMM_THREADS) aux->cnt[i] = __ldg(args.counts + i);
-  __syncthreads();
-  if (warp == 0) {
-    // row groups per expert = ceil(blocks / CG), exclusive prefix over experts; lane handles experts [8*lane, 8*lane+8)
-    int g[8], local = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = lane * 8 + i;
-      g[i] = (e < E) ? (aux->off[e + 1] - aux->off[e] + CG - 1) / CG : 0;
-      local += g[i];
-    }
-    int incl = local;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      int o = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += o;
-    }
-    int run = incl - local;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = lane * 8 + i;
-      if (e < E) aux->grp[e] = run;
-      run += g[i];
-    }
-    if (lane == 31) aux->grp[E] = incl;
-  }
   tc_fence_before();
   __syncthreads();
-  if (CG == 2) cluster_sync_all();  // the partner's barriers exist before anything signals them
   tc_fence_after();
 
   const uint32_t tmem_base = aux->tmem_base;
-  const int total_tiles = aux->grp[E] * NT;
+  const int total_tiles = aux->off[E] * NT;
   volatile int* abort_flag = &aux->abort_flag;
 
   // Each register budget is set inside the branch it governs, so the compiler sees one budget per region.
@@ -201,93 +167,67 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       long long issued = 0;
       bool ok = true;
       for (int tile = group_id; ok && tile < total_tiles; tile += num_groups) {
-        const TileInfo ti = decode_tile<CG>(tile, aux->grp, aux->off, aux->cnt, E, NT, cta_rank);
+        const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
         for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
           ok = mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, abort_flag, args.status, 1, kb);
           if (!ok) break;
           const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
           const uint32_t sB = sbase + C::A_TILES * A_TILE_BYTES;
-          if (CG == 1) {
-            const uint32_t full = smem_u32(&aux->full[stage]);
-            mbar_arrive_expect_tx(full, C::STAGE_BYTES);
-            tma_load_2d(sbase, &tmA, full, kb * 128, ti.mblk * BLOCK_M);
-            if (MODE == 1) {
-              tma_load_2d(sB, &tmB, full, kb * 128, ti.e * (2 * I) + ti.nt * 128);
-              tma_load_2d(sB + 128 * 128, &tmB, full, kb * 128, ti.e * (2 * I) + I + ti.nt * 128);
-            } else {
-              tma_load_2d(sbase + A_TILE_BYTES, &tmA, full, kb * 128, args.R_max + ti.mblk * BLOCK_M);
-              tma_load_2d(sB, &tmB, full, kb * 128, ti.e * H + ti.nt * TILE_N);
-            }
+          const uint32_t full = smem_u32(&aux->full[stage]);
+          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+          tma_load_2d(sbase, &tmA, full, kb * 128, ti.mblk * BLOCK_M);
+          if (MODE == 1) {
+            tma_load_2d(sB, &tmB, full, kb * 128, ti.e * (2 * I) + ti.nt * 128);
+            tma_load_2d(sB + 128 * 128, &tmB, full, kb * 128, ti.e * (2 * I) + I + ti.nt * 128);
           } else {
-            // both CTAs' bytes are counted on the even CTA's barrier; only that CTA posts the expectation
-            const uint32_t full = map_to_cta(smem_u32(&aux->full[stage]), 0);
-            if (leader) mbar_arrive_expect_tx(smem_u32(&aux->full[stage]), 2 * C::STAGE_BYTES);
-            tma_load_2d_pair(sbase, &tmA, full, kb * 128, ti.mblk * BLOCK_M);
-            if (MODE == 1) {
-              // even CTA: W1 rows n0..n0+127 (accumulator columns 0..127); odd CTA: W3 rows (columns 128..255)
-              tma_load_2d_pair(sB, &tmB, full, kb * 128, ti.e * (2 * I) + cta_rank * I + ti.nt * 128);
-            } else {
-              tma_load_2d_pair(sbase + A_TILE_BYTES, &tmA, full, kb * 128, args.R_max + ti.mblk * BLOCK_M);
-              tma_load_2d_pair(sB, &tmB, full, kb * 128, ti.e * H + ti.nt * TILE_N + cta_rank * 128);
-            }
+            tma_load_2d(sbase + A_TILE_BYTES, &tmA, full, kb * 128, args.R_max + ti.mblk * BLOCK_M);
+            tma_load_2d(sB, &tmB, full, kb * 128, ti.e * H + ti.nt * TILE_N);
           }
           ++issued;
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok && (CG == 1 || leader)) {
+      if (!ok) {
         // Drain: every load already issued completes on its own; wait (bounded) so none lands after the CTA exits.
         for (int s = 0; s < C::STAGES; ++s) {
           long long n_s = issued / C::STAGES + ((issued % C::STAGES) > s ? 1 : 0);  // loads issued to stage s
           if (n_s == 0) continue;
           uint32_t par = static_cast<uint32_t>((n_s - 1) & 1);
-          for (int spin = 0; spin < (1 << 20); ++spin)
+          for (int spin = 0; spin < DRAIN_POLLS; ++spin)
             if (mbar_try_wait(smem_u32(&aux->full[s]), par)) break;
         }
       }
     }
     __syncwarp();
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer (one thread; even CTA of a pair)
-    if (lane == 0 && leader) {
-      constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M * CG, TILE_N);
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M, TILE_N);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = group_id; ok && tile < total_tiles; tile += num_groups) {
         for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
-          ok = mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb);
-          if (!ok) break;
-          ok = mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb);
-          if (!ok) break;
-          tc_fence_after();
+          // operands first (they landed several chunks ago), the TMEM stage last: its hand-back is the critical
+          // signal, and everything that can be prepared is ready when it comes
           const uint32_t sbase = tiles_addr + stage * C::STAGE_BYTES;
           const uint32_t d = tmem_base + static_cast<uint32_t>(acc * TILE_N);
           const uint64_t a0 = umma_desc_sw128(sbase);
           const uint64_t b0 = umma_desc_sw128(sbase + C::A_TILES * A_TILE_BYTES);
-          if (CG == 1) {
+          ok = mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb);
+          if (!ok) break;
+          ok = mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a0 + 2 * k4, b0 + 2 * k4, IDESC, k4 > 0 ? 1u : 0u);
-            if (MODE == 2) {
-              const uint64_t a1 = umma_desc_sw128(sbase + A_TILE_BYTES);
+          for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a0 + 2 * k4, b0 + 2 * k4, IDESC, k4 > 0 ? 1u : 0u);
+          if (MODE == 2) {
+            const uint64_t a1 = umma_desc_sw128(sbase + A_TILE_BYTES);
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a1 + 2 * k4, b0 + 2 * k4, IDESC, 1u);
-            }
-            tc_commit(smem_u32(&aux->empty[stage]));
-            tc_commit(smem_u32(&aux->tfull[acc]));
-          } else {
-#pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8_pair(d, a0 + 2 * k4, b0 + 2 * k4, IDESC, k4 > 0 ? 1u : 0u);
-            if (MODE == 2) {
-              const uint64_t a1 = umma_desc_sw128(sbase + A_TILE_BYTES);
-#pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8_pair(d, a1 + 2 * k4, b0 + 2 * k4, IDESC, 1u);
-            }
-            // completion is signalled in both CTAs: the stage is free for both producers, the partials are ready
-            // for both promotion groups
-            tc_commit_pair(smem_u32(&aux->empty[stage]), 3);
-            tc_commit_pair(smem_u32(&aux->tfull[acc]), 3);
+            for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a1 + 2 * k4, b0 + 2 * k4, IDESC, 1u);
           }
+          tc_commit(smem_u32(&aux->empty[stage]));
+          tc_commit(smem_u32(&aux->tfull[acc]));
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           acc ^= 1;
           if (acc == 0) acc_phase ^= 1u;
@@ -302,16 +242,13 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;       // TMEM lane quarter this warp may read
     const int h = warp >> 2;      // column half
     const int r_in_tile = q * 32 + lane;
-    // hand-backs of TMEM stages go to the MMA issuer's barrier, which lives in the even CTA
-    const uint32_t tempty_addr[2] = {
-        (CG == 2) ? map_to_cta(smem_u32(&aux->tempty[0]), 0) : smem_u32(&aux->tempty[0]),
-        (CG == 2) ? map_to_cta(smem_u32(&aux->tempty[1]), 0) : smem_u32(&aux->tempty[1])};
+    const uint32_t tempty_addr[2] = {smem_u32(&aux->tempty[0]), smem_u32(&aux->tempty[1])};
     int acc = 0;
     uint32_t acc_phase = 0;
     int tile_iter = 0;
     bool ok = true;
     for (int tile = group_id; ok && tile < total_tiles; tile += num_groups, ++tile_iter) {
-      const TileInfo ti = decode_tile<CG>(tile, aux->grp, aux->off, aux->cnt, E, NT, cta_rank);
+      const TileInfo ti = decode_tile(tile, aux->off, aux->cnt, E, NT);
       const int row = ti.mblk * BLOCK_M + r_in_tile;
       const bool valid = (ti.m_local * BLOCK_M + r_in_tile) < ti.cnt;
       // rows past the expert's last block (odd CTA of an incomplete pair) can lie outside the workspace: clamp reads
@@ -358,11 +295,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tmem_ld64(taddr + col, tmp);
           tc_wait_ld();
           if (run == 1) {
-            // all of this warp's reads of the stage are complete: hand it back to the MMA issuer
+            // all of this warp's reads of the stage are complete (tcgen05.wait::ld is warp-synchronous): hand it back
+            // to the MMA issuer
             tc_fence_before();
-            __syncwarp();
             if (lane == 0) {
-              if (CG == 2) mbar_arrive_cluster(tempty_addr[acc]); else mbar_arrive(tempty_addr[acc]);
+              mbar_arrive_relaxed(tempty_addr[acc]);
             }
           }
           const float2 sc2 = make_float2(sc, sc);
@@ -465,11 +402,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (CG == 2) cluster_sync_all();  // no CTA leaves while its partner may still signal its barriers or use its TMEM
   if (warp == MMA_WARP) {
     __syncwarp();
     tc_fence_after();
-    if (CG == 2) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -510,13 +446,12 @@ int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, 
 template <int MODE>
 static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
   if (p->T == 0) return B200MOE_OK;
-  constexpr int CG = CTA_GROUP;
   static bool attr_set[64] = {};
   int dev = 0;
   B200MOE_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr size_t smem = gemm_smem_bytes<MODE, CG>();
+  constexpr size_t smem = gemm_smem_bytes<MODE>();
   if (dev < 64 && !attr_set[dev]) {
-    B200MOE_CUDA_TRY(cudaFuncSetAttribute(k_grouped_gemm<MODE, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200MOE_CUDA_TRY(cudaFuncSetAttribute(k_grouped_gemm<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(smem)));
     attr_set[dev] = true;
   }
@@ -535,8 +470,8 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
   a.partial = nullptr;
   a.E_local = p->E_local;
   a.R_max = ws->R_max;
-  // weight boxes: 128 rows everywhere except the single-CTA GEMM2, which takes its 256 W2 rows in one box
-  const uint32_t b_box_rows = (MODE == 2 && CG == 1) ? TILE_N : 128;
+  // weight boxes: GEMM1 takes 128 W1 rows and 128 W3 rows as two boxes, GEMM2 its 256 W2 rows in one
+  const uint32_t b_box_rows = (MODE == 2) ? TILE_N : 128;
   if (MODE == 1) {
     if ((rc = make_map_u8(&tmA, ws->a_sorted, static_cast<uint64_t>(ws->R_max), H, BLOCK_M))) return rc;
     if ((rc = make_map_u8(&tmB, p->gemm1_weights, static_cast<uint64_t>(p->E_local) * 2 * I, H, b_box_rows))) return rc;
@@ -548,13 +483,7 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
     a.row_scale = ws->inter_scale;
     a.w_scale = p->gemm2_weights_scale;
   }
-  const int grid = num_sms / CG * CG;
-  if (CG == 2) {
-    B200MOE_CUDA_TRY(launch_pdl_cluster(k_grouped_gemm<MODE, CG>, dim3(grid), dim3(GEMM_THREADS), smem, st, 2, tmA,
-                                        tmB, a));
-  } else {
-    B200MOE_CUDA_TRY(launch_pdl(k_grouped_gemm<MODE, CG>, dim3(grid), dim3(GEMM_THREADS), smem, st, tmA, tmB, a));
-  }
+  B200MOE_CUDA_TRY(launch_pdl(k_grouped_gemm<MODE>, dim3(num_sms), dim3(GEMM_THREADS), smem, st, tmA, tmB, a));
   return B200MOE_OK;
 }
 

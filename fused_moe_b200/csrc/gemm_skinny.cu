@@ -195,7 +195,7 @@ __device__ __forceinline__ bool run_item(const GemmArgs& args, Aux* aux, const T
     // this warp's reads of the stage are complete: hand it back to the MMA issuer
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[ps.acc]));
+    if (lane == 0) mbar_arrive_relaxed(smem_u32(&aux->tempty[ps.acc]));
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
       a0[j] = __fmaf_rn(__uint_as_float(t0[j]), xs[j] * w0, a0[j]);
@@ -433,7 +433,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             long long n_s = issued / C::STAGES + ((issued % C::STAGES) > s ? 1 : 0);
             if (n_s == 0) continue;
             uint32_t par = static_cast<uint32_t>((n_s - 1) & 1);
-            for (int spin = 0; spin < (1 << 20); ++spin)
+            for (int spin = 0; spin < DRAIN_POLLS; ++spin)
               if (mbar_try_wait(smem_u32(&aux->full[s]), par)) break;
           }
         }

@@ -346,9 +346,9 @@ def kernel_host(routing_logits, routing_bias, hidden_states, hidden_states_scale
 @torch.no_grad()
 def quantize_activations(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 activations [T, 7168] -> (e4m3 [T, 7168], float32 scales [56, T]): the ``hidden_states`` /
-    ``hidden_states_scale`` pair ``kernel`` takes, one scale per token per 128 columns (``b200moe_quantize_act``).
-    The reference has no operator for this step; its profiling script builds the pair with torch
-    (scripts/yjl_ncu.py:413-416)."""
+    ``hidden_states_scale`` pair ``kernel`` takes, one scale per token per 128 columns (``b200moe_quantize_act``):
+    s = max(amax * (1/448), 1e-12), q = e4m3(x * (1/s)).  The reference has no operator for this step; its profiling
+    script builds the pair with torch by multiplying with 448 / amax (scripts/yjl_ncu.py:413-416)."""
     _require(x, "x", torch.bfloat16, (x.shape[0] if torch.is_tensor(x) and x.dim() == 2 else -1, H))
     _require_cuda(x=x)
     x = x.contiguous()

@@ -176,9 +176,10 @@ int b200moe_workspace_init(const b200moe_workspace* ws /* host */, void* stream)
 int b200moe_forward(const b200moe_problem* p /* host */, const b200moe_workspace* ws /* host */, void* stream);
 
 /* Upstream of the layer: bf16 activations [T, 7168] -> e4m3 [T, 7168] and float32 scales [56, T], one scale per token
- * per 128 columns: s = max(amax / 448, 1e-12), q = e4m3(x / s).  Produces the `hidden_states` / `hidden_states_scale`
- * pair that kernel() takes (the reference has no kernel for it; its profiling script builds the pair with torch,
- * scripts/yjl_ncu.py:413-416).  x_bf16 16-byte aligned, q_out 8-byte aligned; needs no workspace. */
+ * per 128 columns: s = max(amax * (1/448), 1e-12), q = e4m3(x * (1/s)), every operation rounded to float32 (round to
+ * nearest even, conversion saturating at +-448).  Produces the `hidden_states` / `hidden_states_scale` pair that
+ * kernel() takes (the reference has no kernel for it; its profiling script builds the pair with torch by multiplying
+ * with 448 / amax, scripts/yjl_ncu.py:413-416).  x_bf16 16-byte aligned, q_out 8-byte aligned; needs no workspace. */
 int b200moe_quantize_act(const void* x_bf16, int32_t T, void* q_out, float* scale_out, void* stream);
 
 /* Stage entry points (unit tests, profiling).  Each runs one stage of b200moe_forward on the same buffers. */

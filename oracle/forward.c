@@ -1,6 +1,6 @@
 /*
- * TEST INFRASTRUCTURE — not part of the product.  Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs
- * may load this code; the CUDA library never calls it.
+ * TEST INFRASTRUCTURE — not part of the product.  Only the tests, the driver's smoke check and bench.py's CPU-baseline
+ * legs may load this code; the CUDA library never calls it.
  *
  * CPU restatement of the reference's fp32-dequant expert path, solution/cuda/binding.py:96-185:
  *   dequantise activations (binding.py:74-78) and the hit experts' weights (binding.py:80-83) to float32,

@@ -1,10 +1,10 @@
 """TEST INFRASTRUCTURE — not part of the product.
 
-ctypes wrapper of the CPU oracle (oracle/route_sort.c, oracle/forward.c): the reference's routing
+ctypes wrapper of the CPU oracle (oracle/route_sort.c, oracle/forward.c, oracle/quant.c): the reference's routing
 (solution/cuda/binding.py:38-61), sort metadata (solution/cuda/binding.py:134-154 and
 solution/python/pure_triton_impl.py:512-531) and fp32-dequant expert path (solution/cuda/binding.py:96-185) restated
-for the host.  Only tests/, ``__graft_entry__.smoke()`` and bench.py's CPU-baseline legs import this module; nothing in
-``fused_moe_b200`` does.
+for the host, plus the activation-quantiser recipe of its profiling script (scripts/yjl_ncu.py:413-416).  Only the
+tests, the driver's smoke check and bench.py's CPU-baseline legs import this module; nothing in ``fused_moe_b200`` does.
 
 Parity pin: tests/golden/*.npz hold outputs of the reference's own ``binding.py`` run on seeded inputs
 (tests/golden/make_golden.py); tests/test_oracle.py checks this oracle against them.
@@ -29,7 +29,7 @@ _lib = None
 
 
 def build(force: bool = False) -> Path:
-    srcs = [ORACLE_DIR / "route_sort.c", ORACLE_DIR / "forward.c", ORACLE_DIR / "Makefile"]
+    srcs = [ORACLE_DIR / "route_sort.c", ORACLE_DIR / "forward.c", ORACLE_DIR / "quant.c", ORACLE_DIR / "Makefile"]
     stale = force or not LIB_PATH.exists() or any(s.stat().st_mtime > LIB_PATH.stat().st_mtime for s in srcs)
     if stale:
         if force:
@@ -51,6 +51,10 @@ def _load():
         lib.oracle_sort.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 5
         lib.oracle_forward.restype = C.c_long
         lib.oracle_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 8 + [C.c_int]
+        lib.oracle_f32_to_e4m3.restype = C.c_uint8
+        lib.oracle_f32_to_e4m3.argtypes = [C.c_float]
+        lib.oracle_quantize_act.restype = None
+        lib.oracle_quantize_act.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         _lib = lib
     return _lib
 
@@ -124,6 +128,22 @@ def kernel(routing_logits, routing_bias, hidden_states, hidden_states_scale, gem
                                             gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
                                             int(local_expert_offset), num_threads)
     return dict(topk_idx=idx, topk_w=w, out_f32=out32, out_bf16=out16, pairs=pairs)
+
+
+def quantize_act(x_bf16: torch.Tensor):
+    """bf16 [T,7168] -> (e4m3 [T,7168], float32 scales [56,T]): s = max(amax/448, 1e-12), q = e4m3(x * (1/s))."""
+    x = _cpu(x_bf16)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == H
+    T = x.shape[0]
+    q = torch.empty((T, H), dtype=torch.uint8)
+    s = torch.empty((H // 128, T), dtype=torch.float32)
+    _load().oracle_quantize_act(x.view(torch.int16).data_ptr(), T, q.data_ptr(), s.data_ptr())
+    return q.view(torch.float8_e4m3fn), s
+
+
+def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
+    lib = _load()
+    return np.array([lib.oracle_f32_to_e4m3(float(v)) for v in np.asarray(x, dtype=np.float32).ravel()], dtype=np.uint8)
 
 
 def sigmoid(x: np.ndarray) -> np.ndarray:

@@ -84,6 +84,65 @@ def test_dispatch_combine_world2():
     assert ret[0][2][1] == ret[1][3][0] and ret[1][2][0] == ret[0][3][1]
 
 
+def _faulty_worker(rank, world, port, ret, fault):
+    """Host-side failures only (no GPU, nothing is made to hang for longer than the group's timeout):
+    "short_send"  rank 1 hands the dispatch all-to-all fewer rows than the split sizes it announced;
+    "leaves"      rank 1 completes one step and then leaves the job; rank 0 starts a second step alone.
+    The other rank must get an exception from the collective, not a wrong result and not an endless wait."""
+    from datetime import timedelta
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=8))
+    outcome = "no error"
+    try:
+        import oracle
+        from fused_moe_b200 import ep, synth
+        inp = synth.make_inputs(T_GLOBAL, 1, seed=17, skew=True, only_experts=[])
+        t_loc = T_GLOBAL // world
+        sl = slice(rank * t_loc, (rank + 1) * t_loc)
+        e_l = 256 // world
+        shard = ep.ExpertParallelMoE(lambda l, b, sc: oracle.route(l, b, sc),
+                                     lambda idx, w, hs, scales: _standin_expert(idx, w, hs, scales, rank * e_l,
+                                                                                (rank + 1) * e_l), rank, world)
+        args = (inp["routing_logits"][sl].contiguous(), inp["routing_bias"], inp["hidden_states"][sl].contiguous(),
+                inp["hidden_states_scale"][:, sl].contiguous(), 2.5)
+        if fault == "short_send" and rank == 1:
+            real_pack = ep.pack_rows
+            ep.pack_rows = lambda tokens, *a: real_pack(tokens[:-3], *a)     # three rows short of the announced count
+        shard.forward(*args)
+        if fault == "leaves":
+            if rank == 1:
+                outcome = "left"
+                return
+            shard.forward(*args)          # the peer is gone
+    except Exception as exc:               # what the test is about: the failure surfaces as an exception
+        outcome = type(exc).__name__
+    finally:
+        ret[rank] = outcome
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("fault", ["short_send", "leaves"])
+def test_host_side_failures_raise_instead_of_hanging(fault):
+    world = 2
+    ret = mp.Manager().dict()
+    port = 29300 + (os.getpid() + (7 if fault == "leaves" else 0)) % 300
+    ctx = mp.spawn(_faulty_worker, args=(world, port, ret, fault), nprocs=world, join=False)
+    import time
+    deadline = time.time() + 120
+    while not ctx.join(timeout=5) and time.time() < deadline:     # join() returns once every rank has exited
+        pass
+    for proc in ctx.processes:
+        assert not proc.is_alive(), "a rank is still waiting two minutes after its peer failed"
+    assert len(ret) == world
+    if fault == "short_send":
+        assert any(v not in ("no error", "left") for v in ret.values()), dict(ret)
+    else:
+        assert ret[1] == "left" and ret[0] not in ("no error", "left"), dict(ret)
+
+
 def test_pack_unpack_roundtrip():
     from fused_moe_b200 import ep, synth
     inp = synth.make_inputs(9, 1, seed=5, only_experts=[])

@@ -115,7 +115,7 @@ def _build_solution(fib, tmp_path, monkeypatch):
 
     def write_then_plant(*args, **kwargs):
         pkg_dir = real_write(*args, **kwargs)
-        if _lib.LIB_PATH.exists():
+        if _lib.LIB_PATH.exists() and (Path(pkg_dir) / "fused_moe_b200").is_dir():   # not the reference's package
             dst = Path(pkg_dir) / "fused_moe_b200" / _lib.LIB_PATH.name
             shutil.copy2(_lib.LIB_PATH, dst)
             os.utime(dst, None)

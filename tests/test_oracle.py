@@ -83,3 +83,29 @@ def test_sort_properties(oracle):
     # scatter_map inverts the placement
     for t, k in zip(*np.nonzero(smap >= 0)):
         assert ids[smap[t, k]] == t and s["sorted_weights"][smap[t, k]] == w[t, k]
+
+
+def test_e4m3_conversion_matches_torch(oracle):
+    """Pins oracle/quant.c's float32 -> e4m3 conversion (round to nearest even) against torch's own on the CPU, over the
+    whole range the quantiser produces (|x| <= 448) including subnormals, ties and both zeros."""
+    torch.manual_seed(0)
+    x = torch.cat([torch.randn(100000) * 100, torch.randn(50000) * 0.01, torch.linspace(-448, 448, 50001),
+                   torch.tensor([0.0, -0.0, 448.0, -448.0, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -9, 2.0 ** -6,
+                                 0.0146484375, 447.9, 2.5 * 2.0 ** -9, 17.0, 18.0, 19.0, 0.40625])]).float()
+    x = x[x.abs() <= 448]
+    want = x.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = oracle.f32_to_e4m3(x.numpy())
+    assert np.array_equal(want, got)
+    assert oracle.f32_to_e4m3(np.array([1e9, -470.0], dtype=np.float32)).tolist() == [0x7E, 0xFE]   # saturating
+
+
+def test_quantiser_restatement_matches_torch_formula(oracle):
+    """oracle.quantize_act against the same specification written with torch ops on the CPU."""
+    x = (synth.normal(9 * 7168, 5, 1).view(9, 7168) * torch.exp(2.0 * synth.normal(9, 5, 7)).view(9, 1)).bfloat16()
+    x[4].zero_()
+    q, s = oracle.quantize_act(x)
+    xb = x.float().view(9, 56, 128)
+    s_t = (xb.abs().amax(dim=2) * (1.0 / 448.0)).clamp_min(1e-12)
+    q_t = (xb * (1.0 / s_t).unsqueeze(2)).to(torch.float8_e4m3fn).view(9, 7168)
+    assert torch.equal(s, s_t.t().contiguous())
+    assert torch.equal(q.view(torch.uint8), q_t.view(torch.uint8))
