@@ -155,7 +155,7 @@ SYMBOLS = {
     "b200moe_ep_exchange_counts": (C.c_int, (C.POINTER(EpPeers), C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
                                              C.c_void_p)),
     "b200moe_ep_pack_peers_planned": (C.c_int, (C.c_void_p,) * 4 + (C.c_int32, C.POINTER(EpPeers), C.c_void_p,
-                                                                   C.c_void_p, C.c_size_t, C.c_void_p)),
+                                                                   C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)),
     "b200moe_set_wait_limit_cycles": (C.c_int, (C.c_int64,)),
     "b200moe_ep_combine": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),

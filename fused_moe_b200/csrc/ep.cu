@@ -14,6 +14,7 @@
 namespace b200moe {
 
 constexpr int EP_RECORD = B200MOE_EP_RECORD_BYTES;  // 7168 + 224 + 32 + 32
+constexpr int ST_BAD_ADDRESS = 4;     // a kernel found a misaligned or out-of-range destination and skipped the access
 
 int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* counts, cudaStream_t st);
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st);
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(256)
 k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale,
                const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int T, const int* __restrict__ counts,
                int world, const int* __restrict__ slot_token, uint8_t* __restrict__ send_rows, const PeerTargets peers,
-               const b200moe_ep_plan* __restrict__ plan) {
+               const b200moe_ep_plan* __restrict__ plan, int cap_recv, int* __restrict__ check) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   pdl_launch_dependents();
@@ -159,6 +160,15 @@ k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hid
         if (s >= seg[j]) d = j;
       const int row0 = plan ? plan->dst_row0[d] : peers.row0[d];
       rec = peers.base[d] + static_cast<size_t>(row0 + (s - seg[d])) * EP_RECORD;
+      if (check && ((reinterpret_cast<uintptr_t>(rec) & 15u) || row0 < 0 || row0 + (s - seg[d]) >= cap_recv)) {
+        // never store through an address that does not add up: record it and skip the record
+        if (lane == 0 && atomicCAS(check, ST_OK, ST_BAD_ADDRESS) == ST_OK) {
+          check[1] = 100 + d;
+          check[2] = row0 + (s - seg[d]);
+          check[3] = static_cast<int>(reinterpret_cast<uintptr_t>(rec) & 0xffff);
+        }
+        continue;
+      }
     }
     const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(tok) * H);
     uint4* dst = reinterpret_cast<uint4*>(rec);
@@ -276,6 +286,15 @@ k_ep_exchange(const ExchangeTargets tg, const int* __restrict__ send_counts, int
       status[2] = cap_recv;
       status[3] = cap_back;
     }
+    for (int x = 0; x < world; ++x)
+      if ((reinterpret_cast<uintptr_t>(tg.back[x]) & 15u) || (reinterpret_cast<uintptr_t>(tg.counts[x]) & 3u)) {
+        if (atomicCAS(status, ST_OK, ST_BAD_ADDRESS) == ST_OK) {
+          status[1] = 200 + x;
+          status[2] = static_cast<int>(reinterpret_cast<uintptr_t>(tg.back[x]) & 0xffff);
+          status[3] = static_cast<int>(reinterpret_cast<uintptr_t>(tg.counts[x]) & 0xffff);
+        }
+        ok = false;
+      }
     plan->ok = ok ? 1 : 0;
     plan->seg_count = world;
     plan->reserved = 0;
@@ -346,12 +365,13 @@ int check_scratch(int32_t T, int32_t world, const void* scratch, size_t scratch_
 }
 int launch_pack(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
                 const float* hidden_states_scale, int32_t T, int32_t world, const Scratch& sc, uint8_t* send_rows,
-                const PeerTargets& peers, const b200moe_ep_plan* plan, cudaStream_t st) {
+                const PeerTargets& peers, const b200moe_ep_plan* plan, int cap_recv, int* check, cudaStream_t st) {
   long long max_pairs = static_cast<long long>(T) * (world < TOP_K ? world : TOP_K);
   int pgrid = static_cast<int>((max_pairs + 7) / 8);
   if (pgrid > 148 * 8) pgrid = 148 * 8;
   B200MOE_CUDA_TRY(launch_pdl(k_pack_records, dim3(pgrid), dim3(256), 0, st, hidden_states, hidden_states_scale,
-                              topk_idx, topk_w, T, sc.counts, world, sc.slot_token, send_rows, peers, plan));
+                              topk_idx, topk_w, T, sc.counts, world, sc.slot_token, send_rows, peers, plan, cap_recv,
+                              check));
   return B200MOE_OK;
 }
 }  // namespace
@@ -388,7 +408,7 @@ int b200moe_ep_dispatch(const int32_t* topk_idx, const float* topk_w, const uint
     return B200MOE_EINVAL;
   PeerTargets none = {};
   return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, world, carve_scratch(scratch, T, world),
-                     send_rows, none, nullptr, static_cast<cudaStream_t>(stream));
+                     send_rows, none, nullptr, 0, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
@@ -407,13 +427,15 @@ int b200moe_ep_pack_peers(const int32_t* topk_idx, const float* topk_w, const ui
     tg.row0[d] = dst_row0[d];
   }
   return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, peers->world,
-                     carve_scratch(scratch, T, peers->world), nullptr, tg, nullptr, static_cast<cudaStream_t>(stream));
+                     carve_scratch(scratch, T, peers->world), nullptr, tg, nullptr, 0, nullptr,
+                     static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
                                   const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers,
-                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, void* stream) {
-  if (!peers || !plan || peers->world < 1 || peers->world > 8) return B200MOE_EINVAL;
+                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, int32_t* status,
+                                  void* stream) {
+  if (!peers || !plan || !status || peers->world < 1 || peers->world > 8) return B200MOE_EINVAL;
   int rc = check_scratch(T, peers->world, scratch, scratch_bytes);
   if (rc || T == 0) return rc;
   if (!topk_idx || !topk_w || !hidden_states || !hidden_states_scale) return B200MOE_EINVAL;
@@ -424,7 +446,8 @@ int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, 
     tg.base[d] = peers->recv_records[d];
   }
   return launch_pack(topk_idx, topk_w, hidden_states, hidden_states_scale, T, peers->world,
-                     carve_scratch(scratch, T, peers->world), nullptr, tg, plan, static_cast<cudaStream_t>(stream));
+                     carve_scratch(scratch, T, peers->world), nullptr, tg, plan, peers->cap_recv, status,
+                     static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers, const int32_t* send_counts, int32_t epoch,

@@ -36,6 +36,7 @@
 // Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the CTA records the failure in the status word,
 // raises a CTA-wide abort flag, drains its outstanding TMA loads, frees TMEM and returns.
 #include <cuda.h>
+#include <cstddef>
 
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -82,7 +83,7 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_off, cons
   return ti;
 }
 
-struct __align__(8) GemmAux {
+struct __align__(16) GemmAux {
   uint64_t full[4];
   uint64_t empty[4];
   uint64_t tfull[2];
@@ -95,8 +96,10 @@ struct __align__(8) GemmAux {
   float amax[2][2][BLOCK_M];
   // GEMM2 epilogue: per promotion warp, 32 rows x 16 columns (+4 padding: conflict-free 16-byte accesses) through which
   // the thread-per-row accumulators are turned into stores of 64 contiguous bytes per row
-  float out_stage[NUM_PROMO_WARPS][32][20];
+  // (16-byte aligned: it is read and written with 16-byte accesses)
+  alignas(16) float out_stage[NUM_PROMO_WARPS][32][20];
 };
+static_assert(offsetof(GemmAux, out_stage) % 16 == 0, "out_stage is accessed with 16-byte vectors");
 
 template <int MODE>
 constexpr size_t gemm_smem_bytes() {

@@ -312,13 +312,14 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const int E = args.E_local;
   constexpr int NT = C::N_TILES;
 
-  // GEMM2 behind GEMM1 in b200moe_forward (args.early_weights): its weights do not depend on GEMM1, and the sort
-  // metadata it needs was complete before GEMM1 passed its own dependency wait.  GEMM1 therefore releases its dependents
-  // only AFTER that wait, and GEMM2 reads the metadata and starts its weight loaders BEFORE its wait; only the roles
-  // that touch what GEMM1 writes (token tiles, scales, tickets, partial sums) wait.  The first stages of W2 are then in
-  // flight while the slowest GEMM1 CTAs still finish.
-  const bool early = (MODE == 2) && args.early_weights != 0;
-  if (MODE == 2) pdl_launch_dependents();
+  // Early weights (args.early_weights, set by b200moe_forward): the expert weights depend on no earlier kernel, and the
+  // sort metadata that names the tiles is complete before this kernel can start at all — GEMM1 follows k_gather, which
+  // releases its dependents only after it has seen the scatter finish, and GEMM2 follows GEMM1, which started under
+  // that same condition.  So the metadata is read and the weight loaders start BEFORE the dependency wait; only the
+  // roles that touch what the predecessor writes (token tiles, scales, tickets, partial sums) wait for it.  The first
+  // weight stages are then in flight while the predecessor (the row gather, or the slowest GEMM1 CTAs) still runs.
+  const bool early = args.early_weights != 0;
+  if (MODE == 2 || early) pdl_launch_dependents();
   if (threadIdx.x == 0) aux->abort_flag = 0;
   if (warp == PRODUCER_WARP && lane == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -342,7 +343,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
   // CTA-local set-up above may overlap the tail of the previous kernel; what that kernel wrote is read from here on
   if (!early) pdl_wait();
-  if (MODE == 1) pdl_launch_dependents();
+  if (MODE == 1 && !early) pdl_launch_dependents();
   for (int i = threadIdx.x; i <= E; i += THREADS) aux->off[i] = __ldg(args.block_offsets + i);
   for (int i = threadIdx.x; i < E; i += THREADS) aux->cnt[i] = __ldg(args.counts + i);
   __syncthreads();
@@ -620,8 +621,10 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
 
 }  // namespace skinny
 
-int launch_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
-  return skinny::launch<1>(p, ws, num_sms, st, false);
+// behind_gather: the launch directly follows launch_gather on the same stream and workspace
+int launch_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,
+                        bool behind_gather) {
+  return skinny::launch<1>(p, ws, num_sms, st, behind_gather);
 }
 // behind_gemm1: the launch directly follows launch_gemm1_skinny on the same stream and workspace
 int launch_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,

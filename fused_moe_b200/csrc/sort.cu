@@ -167,8 +167,11 @@ k_gather(const uint8_t* __restrict__ hidden, long long row_stride, const float* 
          uint8_t* __restrict__ a_sorted, float* __restrict__ a_scale_sorted) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
-  pdl_launch_dependents();
+  // Dependents are released only AFTER this kernel's own dependency wait: a GEMM1 that starts because of this release
+  // may then read the sort metadata (complete, since every CTA here has seen the scatter finish) and stream its first
+  // weight stages while the rows are still being copied; the roles that read those rows wait for this kernel as usual.
   pdl_wait();
+  pdl_launch_dependents();
   const int rows = __ldg(total_blocks) * BLOCK_M;
   for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
     int tok = __ldg(sorted_token_ids + r);
@@ -195,7 +198,7 @@ struct OutSegments {
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
          long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
-         const b200moe_ep_plan* __restrict__ plan, const int* __restrict__ status, int* __restrict__ status_mirror) {
+         const b200moe_ep_plan* __restrict__ plan, int* __restrict__ status, int* __restrict__ status_mirror) {
   const int t = blockIdx.x;
   float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr;
   if (segs.count > 0) {
@@ -229,6 +232,15 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       if (j < plan->seg_count && t >= plan->seg_start[j]) i = j;
     out = nullptr;
     dst_row = plan->seg_base[i] + static_cast<size_t>(t - plan->seg_start[i]) * H;
+    if (reinterpret_cast<uintptr_t>(dst_row) & 15u) {
+      // never store through an address that does not add up: record it (status code 4) and skip the row
+      if (status && threadIdx.x == 0 && atomicCAS(status, 0, 4) == 0) {
+        status[1] = 300 + i;
+        status[2] = t;
+        status[3] = static_cast<int>(reinterpret_cast<uintptr_t>(dst_row) & 0xffff);
+      }
+      return;
+    }
   }
   if (threadIdx.x < TOP_K) {
     s_pos[threadIdx.x] = __ldg(scatter_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
@@ -285,7 +297,7 @@ int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* 
   OutSegments none = {};
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
                               static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none,
-                              static_cast<const b200moe_ep_plan*>(nullptr), static_cast<const int*>(nullptr),
+                              static_cast<const b200moe_ep_plan*>(nullptr), static_cast<int*>(nullptr),
                               static_cast<int*>(nullptr)));
   return B200MOE_OK;
 }
@@ -342,7 +354,7 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   for (int i = 0; i < 9; ++i) segs.start[i] = p->out_seg_start[i];
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
-                              p->output, p->output_f32, segs, p->plan, static_cast<const int*>(ws->status),
+                              p->output, p->output_f32, segs, p->plan, ws->status,
                               ws->status_mirror));
   return B200MOE_OK;
 }

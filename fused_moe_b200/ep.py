@@ -22,8 +22,14 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Optional, Tuple
 
-import torch
-import torch.distributed as dist
+import os
+
+# plain peer mappings only: no NVLink multicast object may ever be bound to the buffers of this module; the switch is
+# read by torch's symmetric memory when it is first used, so it is set before anything can import that
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 H = 7168
 H_BLOCKS = 56
@@ -321,6 +327,9 @@ class CudaExpertParallelMoE:
 
     @staticmethod
     def _status_text(st):
+        if st[0] == 4:
+            return (f"expert-parallel kernel refused a destination address: where={st[1]} row={st[2]} "
+                    f"address bits={st[3]:#x}")
         if st[0] == 3:
             return (f"expert-parallel counts exceed the buffers: rank={st[1]} receive capacity={st[2]} "
                     f"return capacity={st[3]} (do all ranks pass batches within the agreed capacity?)")
@@ -450,7 +459,8 @@ class CudaExpertParallelMoE:
             self._mark("count_exchange")
             _lib.check(lib.b200moe_ep_pack_peers_planned(idx.data_ptr(), w.data_ptr(), hs.data_ptr(), hss.data_ptr(),
                                                          T, peers, plan, b["scratch"].data_ptr(), b["scratch_bytes"],
-                                                         stream), "b200moe_ep_pack_peers_planned")
+                                                         pr["status"].data_ptr(), stream),
+                       "b200moe_ep_pack_peers_planned")
             self._barrier(stream)
             self._mark("records_to_peers")
             wts = self.weights

@@ -314,12 +314,14 @@ int b200moe_ep_barrier(const b200moe_ep_peers* peers /* host */, int32_t epoch, 
  * `rank` of every peer's count matrix, passes the same bounded flag barrier as b200moe_ep_barrier, and then derives
  * *plan (device memory of this rank) from its own, now complete, copy of the matrix.  Replaces an all-gather of the
  * counts plus a device-to-host read.  b200moe_ep_pack_peers_planned is b200moe_ep_pack_peers with the destination rows
- * taken from the plan on the device; b200moe_forward with b200moe_problem.plan set is the receiver. */
+ * taken from the plan on the device (a destination that is misaligned or lies past cap_recv is not stored: status code
+ * 4); b200moe_forward with b200moe_problem.plan set is the receiver. */
 int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers /* host */, const int32_t* send_counts, int32_t epoch,
                                b200moe_ep_plan* plan, int32_t* status, void* stream);
 int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, const uint8_t* hidden_states,
                                   const float* hidden_states_scale, int32_t T, const b200moe_ep_peers* peers /* host */,
-                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, void* stream);
+                                  const b200moe_ep_plan* plan, void* scratch, size_t scratch_bytes, int32_t* status,
+                                  void* stream);
 /* Upper bound, in SM clock cycles, of the waits inside b200moe_ep_barrier and b200moe_ep_exchange_counts for launches
  * made after this call (process-wide; 0 restores the default of about 2 s).  Tests use it to make a wait run out
  * quickly; a deployment can use it to bound how long a lost peer stalls a step. */
