@@ -8,8 +8,8 @@ configurations; at N = 1 a sweep over the reference's batch sizes with its 32 lo
 901, 4096, 11948, 14107, 16384) is added under "sweep".
 
 Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events, inputs resident in HBM, max over ranks);
-`e2e` is the same metric through the public host-memory call (`kernel_host()`; under expert parallelism copies around
-`shard.forward()`) with the per-step tensors starting in pinned host memory and the result copied back (expert weights
+`e2e` is the same metric through the public host-memory call (`kernel_host()`; under expert parallelism the shard's
+`forward_host()`) with the per-step tensors starting in pinned host memory and the result copied back (expert weights
 are layer parameters and stay resident).  `roofline` describes the dominant kernel (GEMM1+SwiGLU) from its own
 CUDA-event timing against an FP8 tensor peak MEASURED in this run (one dense e4m3 GEMM through the vendor library).
 
@@ -606,10 +606,9 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
             K.kernel_host(host["routing_logits"], inp["routing_bias"], host["hidden_states"],
                           host["hidden_states_scale"], *pos[4:], out_host)
             return
-        dev_in = {k: v.to(device, non_blocking=True) for k, v in host.items()}
-        o = shard.forward(dev_in["routing_logits"], inp["routing_bias"], dev_in["hidden_states"],
-                          dev_in["hidden_states_scale"], inp["routed_scaling_factor"], out)
-        out_host.copy_(o, non_blocking=True)
+        # the shard's host-memory entry point: two token runs per step, copies of one run under the step of the other
+        shard.forward_host(host["routing_logits"], inp["routing_bias"], host["hidden_states"],
+                           host["hidden_states_scale"], inp["routed_scaling_factor"], out_host, slices=2)
     e2e_ms = timed_loop(e2e_step, steps, 3, world, device)
     rec["e2e"] = dict(value=T_global / (e2e_ms * 1e-3), unit="tokens/s", ms_per_step=e2e_ms,
                       h2d_bytes_per_step=int(sum_over_ranks(h2d, world, device)),

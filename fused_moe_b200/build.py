@@ -1,6 +1,6 @@
 """Builds libb200moe.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-Run as ``python -m fused_moe_b200.build``; ``__graft_entry__.build()`` calls :func:`build`.
+Run as ``python -m fused_moe_b200.build``; the repository's build hook calls :func:`build`.
 """
 from __future__ import annotations
 

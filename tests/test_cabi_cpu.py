@@ -135,17 +135,32 @@ def test_synth_is_reproducible_and_shaped():
     assert a["hidden_states"].float().abs().max() <= 448
 
 
-def test_documented_binding_matches_the_header_mirror():
-    """The ctypes structures printed in INTEGRATION.md (what a maintainer of the reference would paste) have the fields
-    and sizes of the package's own mirrors of b200moe_problem / b200moe_workspace."""
+def test_ctypes_mirrors_match_the_header_layout(tmp_path):
+    """Every structure of include/b200moe.h, as laid out by the C compiler (sizeof and the offset of every field), equals
+    the package's ctypes mirror of it: what crosses the boundary is read the same way on both sides."""
     import ctypes as C
+    import shutil
+    import subprocess
     from pathlib import Path
     from fused_moe_b200 import _lib
-    text = (Path(__file__).resolve().parent.parent / "INTEGRATION.md").read_text()
-    code = text[text.index("class Problem(C.Structure)"):text.index("_lib.b200moe_workspace_bytes.argtypes")]
-    ns = {"C": C}
-    exec(code, ns)
-    for name in ("Problem", "Workspace"):
-        doc, own = ns[name], getattr(_lib, name)
-        assert [f[0] for f in doc._fields_] == [f[0] for f in own._fields_]
-        assert C.sizeof(doc) == C.sizeof(own)
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    root = Path(__file__).resolve().parent.parent
+    pairs = {"b200moe_problem": _lib.Problem, "b200moe_workspace": _lib.Workspace, "b200moe_ep_peers": _lib.EpPeers,
+             "b200moe_ep_plan": _lib.EpPlan}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "b200moe.h"', 'int main(void) {']
+    for cname, mirror in pairs.items():
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-I", str(root / "include"), str(src), "-o", str(exe)], check=True)
+    got = dict(l.split() for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs.items():
+        assert int(got[cname]) == C.sizeof(mirror), cname
+        for field, _ in mirror._fields_:
+            assert int(got[f"{cname}.{field}"]) == getattr(mirror, field).offset, f"{cname}.{field}"

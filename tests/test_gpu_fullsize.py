@@ -1,4 +1,4 @@
-"""GPU, BASELINE.json's prefill sizes (T = 4096 and 16384, 32 local experts, skewed router; and the bench's headline
+"""GPU, the prefill sizes of the benchmark configurations (T = 4096 and 16384, 32 local experts, skewed router; and the bench's headline
 configuration, T = 16384 with all 256 experts local): the oracle cannot run the
 whole layer at these sizes in seconds, so parity is checked through size-independent properties —
   * routing and the complete sort metadata bit-exact against the oracle (both are cheap on the CPU);

@@ -330,7 +330,27 @@ def test_expert_parallel_shard_world1(moe, transport):
         assert torch.equal(got, want), f"T={T}"
         send, recv = shard.last_splits
         assert send == [T] and recv == [T] and shard.last_records.shape == (T, 7456)
+    # the same (last) batch from pinned host memory, two runs pipelined over the copy streams: identical rows
+    host = {k: cur[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
+    out_h = shard.forward_host(host["routing_logits"], cur["routing_bias"], host["hidden_states"],
+                               host["hidden_states_scale"], cur["routed_scaling_factor"], slices=2)
+    torch.cuda.synchronize()
+    shard.check_status()
+    assert out_h.is_pinned() and torch.equal(out_h, want.cpu())
     if transport == "peer":
+        # a receive buffer of more than 32 chunks of 32 rows: the sort then runs its separate scan kernel, and both it and
+        # the scatter must ignore the rows past the received count
+        big = ep.make_cuda_shard(shard.weights, rank=0, world=1, transport="peer", max_tokens_per_rank=2048)
+        cur = synth.make_inputs(1200, 32, seed=21, local_expert_offset=64, skew=True, device="cuda", weights=inp)
+        want = moe.kernel(**cur).clone()
+        for _ in range(2):
+            big._peer_setup(1200, torch.device("cuda", torch.cuda.current_device()))
+            big._peer["recv"][1200:].fill_(0xFF)
+            got = big.forward(cur["routing_logits"], cur["routing_bias"], cur["hidden_states"],
+                              cur["hidden_states_scale"], cur["routed_scaling_factor"])
+            moe.check_status()
+            big.check_status()
+            assert torch.equal(got, want)
         pl = shard.read_plan()
         assert pl.ok == 1 and pl.n_recv == 412 and pl.n_send == 412 and pl.seg_start[1] == 412 and pl.dst_row0[0] == 0
         with pytest.raises(ValueError):             # beyond the capacity agreed at the first call
