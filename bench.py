@@ -83,6 +83,8 @@ def parse_args():
     ap.add_argument("--ref-gpu-budget", type=float, default=240.0,
                     help="wall-clock seconds the reference's own GPU path may use (autotune included); 0 = skip")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the oracle / transport check")
+    ap.add_argument("--only-quantiser", action="store_true",
+                    help="time only the activation quantiser (the sweep's last entry) and print it; for profiling")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -876,7 +878,11 @@ def main():
     sys.stdout.flush()
     _RESULT_FD = os.dup(1)
     os.dup2(2, 1)
-    if args.impl == "reference":
+    if args.only_quantiser:
+        from fused_moe_b200 import kernel as K
+        torch.cuda.set_device(0)
+        emit(quantiser_line(K, torch.device("cuda", 0), load_peaks()))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -21,7 +21,10 @@ struct GemmArgs {
   float* partial;            // token-minor kernels: partial sums of shared tiles, two slots per CTA
   int E_local;
   int R_max;
-  int early_weights;         // token-minor GEMM2 launched right behind token-minor GEMM1: see gemm_skinny.cu
+  int early_weights;         // token-minor kernels inside b200moe_forward: weight stream starts before the dependency
+                             // wait, see gemm_skinny.cu
+  const uint8_t* next_weights;  // token-minor GEMM1 inside b200moe_forward: the W2 tensor of the GEMM2 that follows (its
+                                // first chunks are asked into L2 while this kernel finishes), else NULL
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
