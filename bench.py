@@ -297,6 +297,33 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
     return res, pairs, active, blocks
 
 
+def time_planned_reduce(K, shard, E_local, offset, reps=5):
+    """us per launch of b200moe_reduce on the workspace the shard's last step left behind, with the step's device-side
+    plan: the rows go to the peers exactly as in the step."""
+    from fused_moe_b200 import _lib
+    from fused_moe_b200.kernel import _workspace
+    lib = _lib.load()
+    pr = shard._peer
+    recv = pr["recv"]
+    dev = recv.device
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = _workspace(dev, recv.shape[0], E_local, stream)
+    p = _lib.Problem()
+    _lib.check(lib.b200moe_ep_record_layout(recv.data_ptr(), recv.shape[0], C.byref(p)), "record_layout")
+    p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
+    p.plan = pr["plan"].data_ptr()
+    torch.cuda.synchronize()
+    barrier(shard.world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        _lib.check(lib.b200moe_reduce(C.byref(p), C.byref(ws.struct), stream), "b200moe_reduce")
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(shard.world)
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
 def quantiser_line(K, device, peaks, T=16384, reps=20):
     """The activation quantiser upstream of the layer (bf16 -> e4m3 + scales), timed alone: HBM-bound, 14 336 B read +
     7 392 B written per token (352 MB at T = 16384, above L2)."""
@@ -626,6 +653,10 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
         rec["ep_transport"] = shard.transport
         shard.check_status()
         shard.profile = False
+        if shard.transport == "peer":
+            # the last kernel of the receiver alone: weighted sums of the received records' rows, stored straight into
+            # the home ranks' buffers over NVLink (every rank at the same time, as in a step; same values as the step)
+            rec["ep_phase_us"]["reduce_with_return_alone"] = round(time_planned_reduce(K, shard, E_local, offset), 1)
         recs = shard.last_records
         st, pairs, active, blocks = stage_times(K, inp, recs.shape[0], E_local, offset, records=recs)
     rec.update(stage_us=st, pairs=pairs, active_experts=active, row_blocks=blocks)

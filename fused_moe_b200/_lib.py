@@ -83,7 +83,7 @@ class EpPlan(C.Structure):
         ("seg_count", C.c_int32),
         ("seg_start", C.c_int32 * 9),
         ("dst_row0", C.c_int32 * 8),
-        ("reserved", C.c_int32),
+        ("rank", C.c_int32),
         ("seg_base", C.c_void_p * 8),
         ("matrix", C.c_int32 * 64),
     ]

@@ -23,7 +23,7 @@ int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStr
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_quantize_act(const void*, int, void*, float*, int, cudaStream_t);
-int launch_gemm1_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool, bool);
+int launch_gemm1_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool);
 int launch_gemm2_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool);
 int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gemv1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
@@ -279,7 +279,7 @@ int b200moe_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, 
     return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
-  return launch_gemm1_skinny(p, ws, sms, static_cast<cudaStream_t>(stream), false, false);
+  return launch_gemm1_skinny(p, ws, sms, static_cast<cudaStream_t>(stream), false);
 }
 
 int b200moe_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
@@ -377,7 +377,7 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   // Few rows per expert (8 T / 256 per expert on average): token-minor tiles, bound by streaming the weights; else
   // 128-token tiles.  Both kernels are correct for every batch; the choice is about speed only.
   if (p->T <= B200MOE_SKINNY_MAX_T) {
-    if ((rc = launch_gemm1_skinny(p, ws, sms, st, after_gather, true))) return rc;
+    if ((rc = launch_gemm1_skinny(p, ws, sms, st, after_gather))) return rc;
     if ((rc = launch_gemm2_skinny(p, ws, sms, st, true))) return rc;
   } else {
     if ((rc = launch_gemm1(p, ws, sms, st))) return rc;

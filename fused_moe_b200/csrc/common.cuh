@@ -143,8 +143,6 @@ __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Ask for one 128-byte line to be brought into L2 (a hint: no destination, nothing to wait for).
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // Ask for the box to be brought into L2 only: no shared-memory destination, no completion to wait for.
 __device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(

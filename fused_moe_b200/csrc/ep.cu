@@ -148,7 +148,11 @@ k_pack_records(const uint8_t* __restrict__ hidden, const float* __restrict__ hid
   seg[8] = total;
   if (world > 8)
     for (int d = 8; d < world; ++d) total += __ldg(counts + d);
-  for (int s = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); s < total; s += gridDim.x * warps_per_cta) {
+  // Peer stores: every rank starts with the records for the NEXT rank and wraps around.  In destination order all ranks
+  // would write to rank 0 first, then all to rank 1, ...: one receiver's NVLink ingress shared by every sender.
+  const int rot = (plan && !send_rows) ? seg[(plan->rank + 1) % world] : 0;
+  for (int s0 = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); s0 < total; s0 += gridDim.x * warps_per_cta) {
+    const int s = (s0 + rot < total) ? s0 + rot : s0 + rot - total;
     const int tok = __ldg(slot_token + s);
     uint8_t* rec;
     if (send_rows) {
@@ -297,7 +301,7 @@ k_ep_exchange(const ExchangeTargets tg, const int* __restrict__ send_counts, int
       }
     plan->ok = ok ? 1 : 0;
     plan->seg_count = world;
-    plan->reserved = 0;
+    plan->rank = rank;
     int n_recv = 0, n_send = 0;
     for (int s = 0; s < 8; ++s) {
       plan->seg_start[s] = n_recv;

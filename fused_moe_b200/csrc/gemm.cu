@@ -470,7 +470,6 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
   a.tile_ctr = nullptr;
   a.weights = nullptr;
   a.early_weights = 0;
-  a.next_weights = nullptr;
   a.partial = nullptr;
   a.E_local = p->E_local;
   a.R_max = ws->R_max;

@@ -23,8 +23,6 @@ struct GemmArgs {
   int R_max;
   int early_weights;         // token-minor kernels inside b200moe_forward: weight stream starts before the dependency
                              // wait, see gemm_skinny.cu
-  const uint8_t* next_weights;  // token-minor GEMM1 inside b200moe_forward: the W2 tensor of the GEMM2 that follows (its
-                                // first chunks are asked into L2 while this kernel finishes), else NULL
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {

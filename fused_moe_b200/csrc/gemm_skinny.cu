@@ -544,23 +544,6 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           if (++arr_stage == C::STAGES) arr_stage = 0;
         }
       }
-      if (MODE == 1 && ok && args.next_weights) {
-        // This CTA's weight stream has ended, but the CTA lives on for some microseconds (last chunks, epilogue, fix-up of
-        // shared tiles) and GEMM2 cannot start on this SM before it exits: HBM would idle.  Ask L2 for the first chunks
-        // of the W2 rows that the CTA of this index streams first in GEMM2 (same deal, computed from the same metadata).
-        using C2 = Cfg<2>;
-        const Deal d2 = make_deal(aux->grp[E] * C2::N_TILES, C2::K_CHUNKS, static_cast<int>(gridDim.x));
-        const long long ub2 = d2.begin(blockIdx.x), ue2 = d2.begin(blockIdx.x + 1);
-        const long long vw2 = static_cast<long long>(d2.rounds) * C2::K_CHUNKS;
-        if (vw2 + (ue2 - ub2) > 0) {
-          const Item it2 = deal_item(d2, C2::K_CHUNKS, static_cast<int>(blockIdx.x), 0, vw2, ub2, ue2);
-          const Tile t2 = decode_tile(it2.tile, aux, E, C2::N_TILES);
-          const int n_pf = (it2.kb1 - it2.kb0) < C2::STAGES ? (it2.kb1 - it2.kb0) : C2::STAGES;
-          const uint8_t* w2 = args.next_weights + (static_cast<size_t>(t2.e) * H + t2.nt * 256) * I + it2.kb0 * 128;
-          for (int r = lt; r < 256; r += NUM_LOADER_WARPS * 32)
-            for (int c = 0; c < n_pf; ++c) prefetch_l2(w2 + static_cast<size_t>(r) * I + c * 128);
-        }
-      }
     }
 #endif
   } else {
@@ -593,8 +576,7 @@ k_grouped_gemm_skinny(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 }
 
 template <int MODE>
-static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st, bool early,
-                  bool gemm2_follows) {
+static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st, bool early) {
   if (p->T == 0) return B200MOE_OK;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -620,7 +602,6 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
   a.partial = ws->gemm_partial;
   a.early_weights = early ? 1 : 0;
   a.weights = static_cast<const uint8_t*>(MODE == 1 ? p->gemm1_weights : p->gemm2_weights);
-  a.next_weights = (MODE == 1 && gemm2_follows) ? p->gemm2_weights : nullptr;
   if (!a.tile_ctr || !a.partial) return B200MOE_EWORKSPACE;
   if (MODE == 1) {
     if ((rc = make_map_u8(&tmX, ws->a_sorted, static_cast<uint64_t>(ws->R_max), H, X_BOX_ROWS))) return rc;
@@ -640,16 +621,15 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
 
 }  // namespace skinny
 
-// behind_gather: the launch directly follows launch_gather on the same stream and workspace;
-// gemm2_follows: launch_gemm2_skinny comes next on the same stream and workspace
+// behind_gather: the launch directly follows launch_gather on the same stream and workspace
 int launch_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,
-                        bool behind_gather, bool gemm2_follows) {
-  return skinny::launch<1>(p, ws, num_sms, st, behind_gather, gemm2_follows);
+                        bool behind_gather) {
+  return skinny::launch<1>(p, ws, num_sms, st, behind_gather);
 }
 // behind_gemm1: the launch directly follows launch_gemm1_skinny on the same stream and workspace
 int launch_gemm2_skinny(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,
                         bool behind_gemm1) {
-  return skinny::launch<2>(p, ws, num_sms, st, behind_gemm1, false);
+  return skinny::launch<2>(p, ws, num_sms, st, behind_gemm1);
 }
 
 }  // namespace b200moe

@@ -69,7 +69,14 @@ int launch_quantize_act(const void* x, int T, void* q, float* scale, int num_sms
   if (T == 0) return B200MOE_OK;
   const long long total = static_cast<long long>(T) * H_BLOCKS;
   long long ctas = (total + 63) / 64;   // 16 half-warps x 4 blocks per CTA and iteration
-  const long long cap = static_cast<long long>(num_sms) * 8;   // 8 resident CTAs of 256 threads per SM
+  // one full wave of resident CTAs (a grid of 8 per SM ran as 1.6 waves of the 5 that fit at 43 registers per thread)
+  static int resident = 0;
+  if (resident == 0) {
+    int n = 0;
+    B200MOE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_quantize_act, 256, 0));
+    resident = n > 0 ? n : 1;
+  }
+  const long long cap = static_cast<long long>(num_sms) * resident;
   if (ctas > cap) ctas = cap;
   B200MOE_CUDA_TRY(launch_pdl(k_quantize_act, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, st,
                               static_cast<const uint4*>(x), T, static_cast<uint2*>(q), scale));

@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
          long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
          const b200moe_ep_plan* __restrict__ plan, int* __restrict__ status, int* __restrict__ status_mirror) {
-  const int t = blockIdx.x;
+  int t = blockIdx.x;
   float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr;
   if (segs.count > 0) {
     // rows of segment i go to segs.base[i], which may be memory of another GPU (plain 16-byte stores)
@@ -225,7 +225,13 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   }
   if (plan) {
     // the row window and the destinations were decided on the device (expert-parallel receiver)
-    if (t >= plan->n_recv) return;
+    const int n = plan->n_recv;
+    if (t >= n) return;
+    // CTAs are scheduled in index order and the rows of one sender are contiguous: start with the rows of the NEXT rank
+    // and wrap around, so that the ranks return rows to different peers at any moment instead of all to rank 0 first
+    // (one receiver's NVLink ingress shared by every sender), then all to rank 1, ...
+    t += plan->seg_start[(plan->rank + 1) % plan->seg_count];
+    if (t >= n) t -= n;
     int i = 0;
 #pragma unroll
     for (int j = 1; j < 8; ++j)

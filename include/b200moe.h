@@ -299,7 +299,8 @@ typedef struct b200moe_ep_plan {
   int32_t seg_count;     /* = world */
   int32_t seg_start[9];  /* received rows [seg_start[s], seg_start[s+1]) come from rank s */
   int32_t dst_row0[8];   /* this rank's records for rank d start at row dst_row0[d] of d's receive buffer */
-  int32_t reserved;
+  int32_t rank;          /* this rank: kernels that store into peers start with the NEXT rank's segment and wrap
+                            around, so that at any moment the ranks write to different peers instead of all to one */
   float* seg_base[8];    /* where the partial rows of segment s go: inside rank s's return buffer */
   int32_t matrix[64];    /* the count matrix, matrix[s*8+d] */
 } b200moe_ep_plan;

@@ -352,7 +352,8 @@ def test_expert_parallel_shard_world1(moe, transport):
             big.check_status()
             assert torch.equal(got, want)
         pl = shard.read_plan()
-        assert pl.ok == 1 and pl.n_recv == 412 and pl.n_send == 412 and pl.seg_start[1] == 412 and pl.dst_row0[0] == 0
+        # the shard's last step was the second run of forward_host: 206 of the 412 tokens
+        assert pl.ok == 1 and pl.n_recv == 206 and pl.n_send == 206 and pl.seg_start[1] == 206 and pl.dst_row0[0] == 0
         with pytest.raises(ValueError):             # beyond the capacity agreed at the first call
             big = synth.make_inputs(513, 32, seed=1, local_expert_offset=64, device="cuda", weights=inp)
             shard.forward(big["routing_logits"], big["routing_bias"], big["hidden_states"], big["hidden_states_scale"],
