@@ -623,25 +623,37 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     if sampler is not None:
         rec["clocks"] = sampler.summary()
 
-    # end to end: per-step tensors start in pinned host memory, result returns to the host
+    # end to end: per-step tensors start in pinned host memory, every step's result returns to the host.  Steps are
+    # queued the way a serving loop would: each call gets its own ready-event and output buffer (two of each, used in
+    # turn) and the host waits for a buffer's event before handing the buffer to a new step, so the copy-in of step
+    # k + 1 and the copy-out of step k - 1 overlap the layer of step k.  Every copy of every step lies inside the
+    # timed region (the closing synchronisation waits for the last copy-out).
     host = {k: inp[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
-    out_host = torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory()
+    outs_host = [torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
     h2d = sum(v.numel() * v.element_size() for v in host.values())
-    d2h = out_host.numel() * 2
+    d2h = outs_host[0].numel() * 2
+    turn = [0]
 
     def e2e_step():
+        j = turn[0] & 1
+        if turn[0] >= 2:
+            ready[j].synchronize()          # the consumer has the rows of step k - 2 before their buffer is reused
+        turn[0] += 1
         if world == 1:
-            # the host-memory entry point: copies in, layer and copies out pipelined over token slices
             K.kernel_host(host["routing_logits"], inp["routing_bias"], host["hidden_states"],
-                          host["hidden_states_scale"], *pos[4:], out_host)
+                          host["hidden_states_scale"], *pos[4:], outs_host[j], ready_event=ready[j])
             return
-        # the shard's host-memory entry point: two token runs per step, copies of one run under the step of the other
         shard.forward_host(host["routing_logits"], inp["routing_bias"], host["hidden_states"],
-                           host["hidden_states_scale"], inp["routed_scaling_factor"], out_host, slices=2)
+                           host["hidden_states_scale"], inp["routed_scaling_factor"], outs_host[j], slices=1,
+                           ready_event=ready[j])
     e2e_ms = timed_loop(e2e_step, steps, 3, world, device)
+    e2e_ok = bool(torch.equal(outs_host[0], outs_host[1]))     # same inputs every step: both buffers hold the result
     rec["e2e"] = dict(value=T_global / (e2e_ms * 1e-3), unit="tokens/s", ms_per_step=e2e_ms,
                       h2d_bytes_per_step=int(sum_over_ranks(h2d, world, device)),
-                      d2h_bytes_per_step=int(sum_over_ranks(d2h, world, device)))
+                      d2h_bytes_per_step=int(sum_over_ranks(d2h, world, device)),
+                      mode="steps queued back to back with ready-events: copies of neighbouring steps overlap the layer")
+    e2e_rows = outs_host[0] if e2e_ok else None
 
     # stage kernels on their own (rank-local problem; at world > 1 this is the home-token slice, for shares only)
     if world == 1:
@@ -662,6 +674,8 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
     rec.update(stage_us=st, pairs=pairs, active_experts=active, row_blocks=blocks)
     step()                        # the workload's result, for the comparisons made outside the timed regions
     torch.cuda.synchronize()
+    # the rows the end-to-end steps delivered to the host are the rows of the device-resident step
+    rec["e2e"]["rows_equal_device_step"] = bool(e2e_rows is not None and torch.equal(e2e_rows, out.cpu()))
     rec["_out"] = out
     if world > 1:
         rec["_shard"] = shard

@@ -440,17 +440,20 @@ class CudaExpertParallelMoE:
 
     @torch.no_grad()
     def forward_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor,
-                     output: Optional[torch.Tensor] = None, slices: int = 2) -> torch.Tensor:
+                     output: Optional[torch.Tensor] = None, slices: int = 2, ready_event=None) -> torch.Tensor:
         """``forward`` for a rank whose tokens live in HOST memory: ``routing_logits``, ``hidden_states``,
         ``hidden_states_scale`` and ``output`` are pinned host tensors (``output=None`` allocates one); the bias is a
         device tensor.  The rank's tokens are cut into ``slices`` equal runs and every run is one complete
         expert-parallel step (so EVERY rank must pass the same ``slices``); the host-to-device copy of run i + 1 and the
         device-to-host copy of run i - 1 go over two side streams and overlap the step on run i.  Rows are independent,
         so the result equals one ``forward`` on all tokens.  Returns ``output`` after queueing everything: the caller's
-        current stream waits for the last copy."""
+        current stream waits for the last copy, unless ``ready_event`` is given — then that event is recorded after the
+        last copy-out, nothing waits for it, and consecutive calls overlap their copies with each other's steps
+        (see ``fused_moe_b200.kernel.kernel_host``)."""
+        from . import kernel as K
         for name, t in (("routing_logits", routing_logits), ("hidden_states", hidden_states),
                         ("hidden_states_scale", hidden_states_scale)):
-            if not torch.is_tensor(t) or t.is_cuda or not t.is_pinned():
+            if not torch.is_tensor(t) or t.is_cuda or (t.numel() > 0 and not t.is_pinned()):   # empty: nothing to pin
                 raise RuntimeError(f"{name} must be a pinned host tensor")
         T = int(routing_logits.shape[0])
         device = routing_bias.device
@@ -459,50 +462,16 @@ class CudaExpertParallelMoE:
         if slices < 1 or (T > 0 and slices > T):
             raise ValueError("slices must be in 1..T")
         if T == 0:
+            if ready_event is not None:
+                ready_event.record(torch.cuda.current_stream(device))
             return output
-        t_slice = (T + slices - 1) // slices
-        hp = getattr(self, "_host_pipe", None)
-        if hp is None or hp["t_slice"] < t_slice or hp["T"] < T:
-            hp = dict(t_slice=t_slice, T=T, h2d=torch.cuda.Stream(device), d2h=torch.cuda.Stream(device),
-                      logits=[torch.empty((t_slice, E_GLOBAL), dtype=torch.float32, device=device) for _ in range(2)],
-                      hs=[torch.empty((t_slice, H), dtype=torch.float8_e4m3fn, device=device) for _ in range(2)],
-                      out=[torch.empty((t_slice, H), dtype=torch.bfloat16, device=device) for _ in range(2)],
-                      scale=torch.empty((H_BLOCKS, T), dtype=torch.float32, device=device))
-            self._host_pipe = hp
-        cur = torch.cuda.current_stream(device)
-        h2d, d2h = hp["h2d"], hp["d2h"]
-        h2d.wait_stream(cur)     # earlier work on the caller's stream may still read the staging buffers
-        d2h.wait_stream(cur)
-        scale_dev = hp["scale"].view(-1)[:H_BLOCKS * T].view(H_BLOCKS, T)
-        with torch.cuda.stream(h2d):
-            scale_dev.copy_(hidden_states_scale, non_blocking=True)
-        done, drained = [], []
-        for i in range(slices):
-            a, b = i * t_slice, min(T, (i + 1) * t_slice)
-            n, k = b - a, i % 2
-            with torch.cuda.stream(h2d):
-                if i >= 2:
-                    h2d.wait_event(done[i - 2])          # the step on run i - 2 has finished reading staging set k
-                hp["logits"][k][:n].copy_(routing_logits[a:b], non_blocking=True)
-                hp["hs"][k][:n].copy_(hidden_states[a:b], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record(h2d)
-            cur.wait_event(arrived)
-            if i >= 2:
-                cur.wait_event(drained[i - 2])           # the copy-out of run i - 2 has finished reading out[k]
-            self.forward(hp["logits"][k][:n], routing_bias, hp["hs"][k][:n], scale_dev[:, a:b].contiguous(),
-                         routed_scaling_factor, hp["out"][k][:n])
-            ev = torch.cuda.Event()
-            ev.record(cur)
-            done.append(ev)
-            with torch.cuda.stream(d2h):
-                d2h.wait_event(ev)
-                output[a:b].copy_(hp["out"][k][:n], non_blocking=True)
-                ev2 = torch.cuda.Event()
-                ev2.record(d2h)
-                drained.append(ev2)
-        cur.wait_stream(d2h)
-        return output
+
+        def layer(logits_dev, hs_dev, scale_dev, out_dev):
+            self.forward(logits_dev, routing_bias, hs_dev, scale_dev, routed_scaling_factor, out_dev)
+
+        with torch.cuda.device(device):
+            pipe = K.HostPipe.get(self.__dict__, "_host_pipe", device, T, (T + slices - 1) // slices)
+            return pipe.run(layer, routing_logits, hidden_states, hidden_states_scale, output, slices, ready_event)
 
     def _forward_peer(self, idx, w, hs, hss, output, T, device, b):
         """Peer transport: nothing below waits for the device or calls a collective."""

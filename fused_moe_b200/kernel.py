@@ -240,37 +240,111 @@ def kernel(
     return _run(T, E_local, offset, scale, logits, bias, hs, hs_scale, w13, w13s, w2, w2s, output, None, None)
 
 
-_host_pipes: Dict[int, dict] = {}
+class HostPipe:
+    """Staging of the host-memory entry points (``kernel_host``, the expert-parallel shard's ``forward_host``): two
+    copy streams and two sets of device buffers (router logits, e4m3 rows, output rows) plus two scale buffers, used in
+    turn.  Which copy or layer call last touched a set is kept as an event ACROSS calls, so a call never waits for more
+    than the buffers it is about to overwrite: with ``ready_event`` the copy-in of call k + 1 runs under the layer of
+    call k and the copy-out of call k under the layer of call k + 1."""
+
+    def __init__(self, device: torch.device, T: int, t_slice: int):
+        self.device, self.T, self.t_slice = device, T, t_slice
+        self.h2d, self.d2h = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.logits = [torch.empty((t_slice, E_GLOBAL), dtype=torch.float32, device=device) for _ in range(2)]
+        self.hs = [torch.empty((t_slice, H), dtype=_FP8, device=device) for _ in range(2)]
+        self.out = [torch.empty((t_slice, H), dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.scale = [torch.empty(H_BLOCKS * T, dtype=torch.float32, device=device) for _ in range(2)]
+        self.done = [None, None]         # the layer has finished reading staging set k
+        self.drained = [None, None]      # the copy-out has finished reading out[k]
+        self.scale_free = [None, None]   # every layer call of the batch that used scale[j] has taken its slice
+        self.runs = 0
+        self.calls = 0
+
+    @staticmethod
+    def get(owner: dict, key, device: torch.device, T: int, t_slice: int) -> "HostPipe":
+        """The pipe kept under ``owner[key]``, replaced by a larger one when the batch outgrows it (after the device
+        has finished with the old buffers)."""
+        pipe = owner.get(key)
+        if pipe is None or pipe.t_slice < t_slice or pipe.T < T:
+            if pipe is not None:
+                torch.cuda.synchronize(device)
+            pipe = HostPipe(device, T, t_slice)
+            owner[key] = pipe
+        return pipe
+
+    def run(self, layer, logits, hs, hs_scale, output, slices: int, ready_event=None):
+        """Queues the whole batch: ``layer(logits_dev, hs_dev, scale_dev, out_dev)`` is called once per run of tokens
+        on the caller's current stream.  Without ``ready_event`` the caller's stream waits for the last copy-out;
+        with it the event is recorded there instead and nothing waits."""
+        T = int(logits.shape[0])
+        t_slice = (T + slices - 1) // slices
+        cur = torch.cuda.current_stream(self.device)
+        h2d, d2h = self.h2d, self.d2h
+        j = self.calls % 2
+        self.calls += 1
+        scale_dev = self.scale[j][:H_BLOCKS * T].view(H_BLOCKS, T)
+        with torch.cuda.stream(h2d):
+            if self.scale_free[j] is not None:
+                h2d.wait_event(self.scale_free[j])
+            scale_dev.copy_(hs_scale, non_blocking=True)
+        last = None
+        for i in range(slices):
+            a, b = i * t_slice, min(T, (i + 1) * t_slice)
+            n, k = b - a, self.runs % 2
+            self.runs += 1
+            with torch.cuda.stream(h2d):
+                if self.done[k] is not None:
+                    h2d.wait_event(self.done[k])
+                self.logits[k][:n].copy_(logits[a:b], non_blocking=True)
+                self.hs[k][:n].copy_(hs[a:b], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(h2d)
+            cur.wait_event(arrived)
+            if self.drained[k] is not None:
+                cur.wait_event(self.drained[k])
+            layer(self.logits[k][:n], self.hs[k][:n], scale_dev[:, a:b].contiguous() if slices > 1 else scale_dev,
+                  self.out[k][:n])
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            self.done[k] = ev
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(ev)
+                output[a:b].copy_(self.out[k][:n], non_blocking=True)
+                last = torch.cuda.Event()
+                last.record(d2h)
+                self.drained[k] = last
+                if ready_event is not None and i == slices - 1:
+                    ready_event.record(d2h)      # the caller's own event: it may re-record it whenever it likes
+        self.scale_free[j] = self.done[(self.runs - 1) % 2]
+        if ready_event is None:
+            cur.wait_event(last)
+        return output
 
 
-def _host_pipe(device: torch.device, T: int, t_slice: int) -> dict:
-    """Copy streams, events and the two sets of staging buffers of ``kernel_host`` (one per device, resized on demand)."""
-    st = _host_pipes.get(device.index)
-    if st is None or st["t_slice"] < t_slice or st["T"] < T:
-        st = dict(t_slice=t_slice, T=T, h2d=torch.cuda.Stream(device), d2h=torch.cuda.Stream(device),
-                  logits=[torch.empty((t_slice, E_GLOBAL), dtype=torch.float32, device=device) for _ in range(2)],
-                  hs=[torch.empty((t_slice, H), dtype=_FP8, device=device) for _ in range(2)],
-                  out=[torch.empty((t_slice, H), dtype=torch.bfloat16, device=device) for _ in range(2)],
-                  scale=torch.empty((H_BLOCKS, T), dtype=torch.float32, device=device))
-        _host_pipes[device.index] = st
-    return st
+_host_pipes: Dict[int, HostPipe] = {}
 
 
 @torch.no_grad()
 def kernel_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
                 gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output=None,
-                slices: Optional[int] = None):
+                slices: Optional[int] = None, ready_event: Optional["torch.cuda.Event"] = None):
     """``kernel`` for activations that live in HOST memory: ``routing_logits``, ``hidden_states``,
     ``hidden_states_scale`` and ``output`` are pinned host tensors (``output=None`` allocates one), the bias and the
-    expert weights are device tensors as in ``kernel``.  The tokens are cut into ``slices`` equal runs (default: chosen
-    from the batch size and the number of local experts, see below) and pipelined over three streams, so the host-to-device copy of run i + 1 and the
-    device-to-host copy of run i - 1 overlap the layer on run i; rows are independent, so the result equals one
-    ``kernel`` call on all tokens bit for bit.  Returns ``output`` after queueing everything: the caller's current
-    stream waits for the last copy, so synchronising that stream (or the device) makes ``output`` valid.
+    expert weights are device tensors as in ``kernel``.  The tokens are cut into ``slices`` equal runs and pipelined
+    over three streams, so the host-to-device copy of run i + 1 and the device-to-host copy of run i - 1 overlap the
+    layer on run i; rows are independent, so the result equals one ``kernel`` call on all tokens bit for bit.
+    Returns ``output`` after queueing everything.
+
+    Without ``ready_event`` the caller's current stream waits for the last copy, so synchronising that stream (or the
+    device) makes ``output`` valid; the default ``slices`` then balances the copies a call cannot hide against the
+    cost of streaming the expert weights once per run.  With ``ready_event`` (a ``torch.cuda.Event``) the event is
+    recorded after the last copy-out and NOTHING waits for it: wait for the event before reading ``output`` or
+    rewriting the input tensors' memory.  Consecutive calls then overlap — the copy-in of the next batch runs under
+    this batch's layer and this batch's copy-out under the next one's — and the default is one run per call.
     The reference has no host-memory entry point (its harness hands ``kernel`` device tensors)."""
     for name, t in (("routing_logits", routing_logits), ("hidden_states", hidden_states),
                     ("hidden_states_scale", hidden_states_scale)):
-        if not torch.is_tensor(t) or t.is_cuda or not t.is_pinned():
+        if not torch.is_tensor(t) or t.is_cuda or (t.numel() > 0 and not t.is_pinned()):   # empty: nothing to pin
             raise RuntimeError(f"{name} must be a pinned host tensor")
     if routing_logits.dim() != 2:
         raise ValueError("routing_logits must be [T, 256]")
@@ -283,10 +357,14 @@ def kernel_host(routing_logits, routing_bias, hidden_states, hidden_states_scale
     elif (not torch.is_tensor(output) or output.is_cuda or not output.is_pinned() or output.dtype != torch.bfloat16
           or tuple(output.shape) != (T, H) or not output.is_contiguous()):
         raise ValueError("output must be a contiguous pinned host bf16 tensor of shape [T, 7168]")
-    if T == 0:
-        return output
     device = gemm1_weights.device
     _require_cuda(gemm1_weights=gemm1_weights)
+    if T == 0:
+        if ready_event is not None:
+            ready_event.record(torch.cuda.current_stream(device))
+        return output
+    if slices is None and ready_event is not None:
+        slices = 1
     if slices is None:
         # Every run streams the expert weights again (~E x 44 MB at ~5 TB/s) while the copies it can hide shrink with
         # the number of runs (22.7 KB per token over a ~55 GB/s host link): the sum is least near sqrt(copy / stream).
@@ -296,51 +374,14 @@ def kernel_host(routing_logits, routing_bias, hidden_states, hidden_states_scale
         slices = max(1, min(8, int(round((copy_s / stream_s) ** 0.5)), T // 1024))
     if slices < 1 or slices > T:
         raise ValueError("slices must be in 1..T")
-    if slices == 1:
-        # nothing to overlap: one copy in, the layer, one copy out, all on the caller's stream
-        with torch.cuda.device(device):
-            out_dev = kernel(logits.to(device, non_blocking=True), routing_bias, hs.to(device, non_blocking=True),
-                             hs_scale.to(device, non_blocking=True), gemm1_weights, gemm1_weights_scale, gemm2_weights,
-                             gemm2_weights_scale, local_expert_offset, routed_scaling_factor)
-            output.copy_(out_dev, non_blocking=True)
-        return output
-    t_slice = (T + slices - 1) // slices
-    pipe = _host_pipe(device, T, t_slice)
-    cur = torch.cuda.current_stream(device)
-    h2d, d2h = pipe["h2d"], pipe["d2h"]
-    h2d.wait_stream(cur)     # earlier work on the caller's stream may still read the staging buffers
-    d2h.wait_stream(cur)
-    scale_dev = pipe["scale"].view(-1)[:H_BLOCKS * T].view(H_BLOCKS, T)
-    with torch.cuda.stream(h2d):
-        scale_dev.copy_(hs_scale, non_blocking=True)
-    done, drained = [], []
-    for i in range(slices):
-        a, b = i * t_slice, min(T, (i + 1) * t_slice)
-        n, k = b - a, i % 2
-        with torch.cuda.stream(h2d):
-            if i >= 2:
-                h2d.wait_event(done[i - 2])          # the layer on run i - 2 has finished reading staging set k
-            pipe["logits"][k][:n].copy_(logits[a:b], non_blocking=True)
-            pipe["hs"][k][:n].copy_(hs[a:b], non_blocking=True)
-            arrived = torch.cuda.Event()
-            arrived.record(h2d)
-        cur.wait_event(arrived)
-        if i >= 2:
-            cur.wait_event(drained[i - 2])           # the copy-out of run i - 2 has finished reading out[k]
-        kernel(pipe["logits"][k][:n], routing_bias, pipe["hs"][k][:n], scale_dev[:, a:b].contiguous(), gemm1_weights,
-               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor,
-               pipe["out"][k][:n])
-        ev = torch.cuda.Event()
-        ev.record(cur)
-        done.append(ev)
-        with torch.cuda.stream(d2h):
-            d2h.wait_event(ev)
-            output[a:b].copy_(pipe["out"][k][:n], non_blocking=True)
-            ev2 = torch.cuda.Event()
-            ev2.record(d2h)
-            drained.append(ev2)
-    cur.wait_stream(d2h)
-    return output
+
+    def layer(logits_dev, hs_dev, scale_dev, out_dev):
+        kernel(logits_dev, routing_bias, hs_dev, scale_dev, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+               gemm2_weights_scale, local_expert_offset, routed_scaling_factor, out_dev)
+
+    with torch.cuda.device(device):
+        pipe = HostPipe.get(_host_pipes, device.index, device, T, (T + slices - 1) // slices)
+        return pipe.run(layer, logits, hs, hs_scale, output, slices, ready_event)
 
 
 @torch.no_grad()

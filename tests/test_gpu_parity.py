@@ -337,6 +337,20 @@ def test_expert_parallel_shard_world1(moe, transport):
     torch.cuda.synchronize()
     shard.check_status()
     assert out_h.is_pinned() and torch.equal(out_h, want.cpu())
+    # and three calls queued back to back, each with its own event instead of a wait on the caller's stream
+    outs = [torch.empty((412, 7168), dtype=torch.bfloat16).pin_memory().fill_(3.0) for _ in range(3)]
+    evs = [torch.cuda.Event() for _ in outs]
+    for o, ev, sl in zip(outs, evs, (1, 2, 1)):
+        shard.forward_host(host["routing_logits"], cur["routing_bias"], host["hidden_states"],
+                           host["hidden_states_scale"], cur["routed_scaling_factor"], o, slices=sl, ready_event=ev)
+    for o, ev in zip(outs, evs):
+        ev.synchronize()
+        assert torch.equal(o, want.cpu())
+    torch.cuda.synchronize()
+    shard.check_status()
+    shard.forward_host(host["routing_logits"], cur["routing_bias"], host["hidden_states"],
+                       host["hidden_states_scale"], cur["routed_scaling_factor"], slices=2)
+    torch.cuda.synchronize()
     if transport == "peer":
         # a receive buffer of more than 32 chunks of 32 rows: the sort then runs its separate scan kernel, and both it and
         # the scatter must ignore the rows past the received count
@@ -417,6 +431,38 @@ def test_host_memory_entry_point_equals_device_call(moe, T, slices):
     assert got.is_pinned() and torch.equal(got, want) and torch.equal(again, want)
     with pytest.raises(RuntimeError):
         moe.kernel_host(**inp)    # device activations
+
+
+def test_host_memory_calls_overlap_with_ready_events(moe):
+    """kernel_host with ready_event: five batches of different sizes and contents are queued back to back without any
+    wait in between (copy-in of one under the layer of the previous, copy-out under the next); each output, read after
+    its own event, has the bytes of kernel() on that batch."""
+    from fused_moe_b200 import synth
+    base = gpu_inputs(1500, 32, 0, 0, True)
+    batches = []
+    for i, (T, seed, slices) in enumerate(((1500, 3, None), (700, 4, 2), (1500, 5, None), (64, 6, None), (1300, 7, 3))):
+        cur = synth.make_inputs(T, 32, seed=seed, local_expert_offset=0, skew=bool(i & 1), device="cuda", weights=base)
+        want = moe.kernel(**cur).cpu()
+        args = dict(cur)
+        args.update({k: cur[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")})
+        batches.append((args, want, slices, torch.empty((T, 7168), dtype=torch.bfloat16).pin_memory().fill_(7.0)))
+    torch.cuda.synchronize()
+    events = [torch.cuda.Event() for _ in batches]
+    for (args, _, slices, out), ev in zip(batches, events):
+        assert moe.kernel_host(**args, output=out, slices=slices, ready_event=ev) is out
+    for (args, want, _, out), ev in zip(batches, events):
+        ev.synchronize()
+        assert torch.equal(out, want)
+    torch.cuda.synchronize()
+    moe.check_status()
+    # an empty batch records the event at once
+    empty = {k: (v[:0] if k in ("routing_logits", "hidden_states") else v) for k, v in batches[0][0].items()}
+    empty["hidden_states_scale"] = torch.empty((56, 0), dtype=torch.float32).pin_memory()
+    empty["routing_logits"] = torch.empty((0, 256), dtype=torch.float32).pin_memory()
+    empty["hidden_states"] = torch.empty((0, 7168), dtype=torch.float8_e4m3fn).pin_memory()
+    ev = torch.cuda.Event()
+    assert moe.kernel_host(**empty, ready_event=ev).shape == (0, 7168)
+    ev.synchronize()
 
 
 def test_interleaved_batch_sizes_share_one_workspace(moe):
