@@ -120,6 +120,47 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// A shared-memory counter as a one-way signal: the writers add with release ordering, one reader polls it with acquire
+// loads until it reaches `target` (bounded like mbar_wait).  A poll is a plain shared-memory load: nothing parks, and
+// the reader sees the last addition a few tens of cycles after it happens.
+__device__ __forceinline__ void red_add_release_shared(uint32_t* counter, uint32_t v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;"
+               ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(counter))), "r"(v)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_shared(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];"
+               : "=r"(v)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p)))
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ bool counter_wait(const uint32_t* counter, uint32_t target, volatile int* abort_flag,
+                                             int* status, int role, int detail) {
+  if (ld_acquire_shared(counter) >= target) return true;
+  long long t0 = 0;
+  uint32_t spins = 0;
+  for (;;) {
+    if (ld_acquire_shared(counter) >= target) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        if (atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT) == ST_OK) {
+          status[1] = static_cast<int>(blockIdx.x);
+          status[2] = role;
+          status[3] = detail;
+        }
+        return false;
+      }
+    }
+  }
+}
+
 // Warp-level form: every lane polls and the warp agrees on the outcome (all lanes polling measured faster on B200
 // than one elected lane with the rest parked at a warp barrier every time: 967 vs 1204 cycles per GEMM chunk; roles
 // that only ever need one thread run their whole loop as lane 0 instead).

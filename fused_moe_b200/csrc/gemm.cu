@@ -22,8 +22,12 @@
 // the hand-back, 170 to re-check the operands), so two stages keep the tensor pipe ~55 % busy: ~970 cycles per 128-K
 // chunk.  Things that were built, measured and did NOT move it: CTA pairs (tcgen05.mma.cta_group::2, each CTA loading
 // half of the weight tile: fewer L2 bytes, but the hand-back then crosses SMs; 485 vs 456 us, also 7 % of pair padding),
-// a second MMA-issuing thread (one per TMEM stage), parking barrier polls with a suspend-time hint, and a relaxed
-// instead of a releasing hand-back arrival.  In isolation the pieces run at 512 (MMA), 320 (promotion, 8 warps) and
+// a second MMA-issuing thread (one per TMEM stage; with it the issuer has slack and the promotion warps are busy
+// ~850 of every ~980 cycles: wake-up, 64-column load, 32 packed FMAs, load, 32 FMAs, nothing overlapped because 128
+// accumulators + 64 loaded values fill the 232 registers), the last promotion warp issuing the next MMAs itself (the
+// issue of four MMAs blocks its thread for ~430 cycles: 38 % slower), parking barrier polls with a suspend-time hint,
+// and a relaxed instead of a releasing hand-back.  The hand-back itself is a shared-memory counter polled by the
+// issuer (2-7 % faster than an mbarrier).  In isolation the pieces run at 512 (MMA), 320 (promotion, 8 warps) and
 // 610-690 (48 KB of loads per SM from L2, all SMs) cycles per chunk, and ~600 when all three run unsynchronised.
 //
 // Warp roles (384 threads): warps 0-7 promote TMEM partials into fp32 registers and run the epilogue (warp w owns TMEM
@@ -87,10 +91,12 @@ struct __align__(16) GemmAux {
   uint64_t full[4];
   uint64_t empty[4];
   uint64_t tfull[2];
-  uint64_t tempty[2];
   uint64_t xbar[2];
   uint32_t tmem_base;
   int abort_flag;
+  // per TMEM stage: promotion warps that have finished reading it, counted up for ever (8 per fill).  The MMA issuer
+  // polls it with plain loads; an mbarrier hand-back measured 2-7 % slower (the issuer's wake-up is on its serial path)
+  uint32_t drained[2];
   int off[E_GLOBAL + 1];
   int cnt[E_GLOBAL];
   float amax[2][2][BLOCK_M];
@@ -124,7 +130,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int num_groups = gridDim.x;
 
   pdl_launch_dependents();
-  if (threadIdx.x == 0) aux->abort_flag = 0;
+  if (threadIdx.x == 0) {
+    aux->abort_flag = 0;
+    aux->drained[0] = 0;
+    aux->drained[1] = 0;
+  }
 
   if (warp == PRODUCER_WARP && lane == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -133,7 +143,6 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&aux->tfull[a]), 1);
-      mbar_init(smem_u32(&aux->tempty[a]), NUM_PROMO_WARPS);
       mbar_init(smem_u32(&aux->xbar[a]), NUM_PROMO_WARPS);
     }
     fence_mbar_init();
@@ -207,7 +216,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t IDESC = umma_idesc_e4m3(BLOCK_M, TILE_N);
       int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t phase = 0;
+      uint32_t chunk = 0;                // chunks issued so far: chunk c is fill number c / 2 of TMEM stage c % 2
       bool ok = true;
       for (int tile = group_id; ok && tile < total_tiles; tile += num_groups) {
         for (int kb = 0; kb < C::K_CHUNKS; ++kb) {
@@ -219,8 +229,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint64_t b0 = umma_desc_sw128(sbase + C::A_TILES * A_TILE_BYTES);
           ok = mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, args.status, 3, kb);
           if (!ok) break;
-          ok = mbar_wait(smem_u32(&aux->tempty[acc]), acc_phase ^ 1u, abort_flag, args.status, 2, kb);
+          ok = counter_wait(&aux->drained[acc], (chunk >> 1) * NUM_PROMO_WARPS, abort_flag, args.status, 2, kb);
           if (!ok) break;
+          ++chunk;
           tc_fence_after();
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) tc_mma_f8(d, a0 + 2 * k4, b0 + 2 * k4, IDESC, k4 > 0 ? 1u : 0u);
@@ -233,7 +244,6 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_commit(smem_u32(&aux->tfull[acc]));
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           acc ^= 1;
-          if (acc == 0) acc_phase ^= 1u;
         }
       }
     }
@@ -245,7 +255,6 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;       // TMEM lane quarter this warp may read
     const int h = warp >> 2;      // column half
     const int r_in_tile = q * 32 + lane;
-    const uint32_t tempty_addr[2] = {smem_u32(&aux->tempty[0]), smem_u32(&aux->tempty[1])};
     int acc = 0;
     uint32_t acc_phase = 0;
     int tile_iter = 0;
@@ -301,9 +310,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // all of this warp's reads of the stage are complete (tcgen05.wait::ld is warp-synchronous): hand it back
             // to the MMA issuer
             tc_fence_before();
-            if (lane == 0) {
-              mbar_arrive_relaxed(tempty_addr[acc]);
-            }
+            if (lane == 0) red_add_release_shared(&aux->drained[acc], 1u);
           }
           const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
