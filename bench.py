@@ -312,6 +312,7 @@ def time_planned_reduce(K, shard, E_local, offset, reps=5):
     _lib.check(lib.b200moe_ep_record_layout(recv.data_ptr(), recv.shape[0], C.byref(p)), "record_layout")
     p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
     p.plan = pr["plan"].data_ptr()
+    p.partial_format = _lib.PARTIAL_HALF if shard.half_rows else _lib.PARTIAL_F32
     torch.cuda.synchronize()
     barrier(shard.world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -663,6 +664,7 @@ def measure_workload(K, name, T_global, E1, skew, args, rank, world, device, pea
         step()
         rec["ep_phase_us"] = {k: round(v, 1) for k, v in shard.phase_times().items()}
         rec["ep_transport"] = shard.transport
+        rec["ep_partial_rows"] = "half (8 x float16 + scale byte, 15232 B/row)" if shard.half_rows else "float32"
         shard.check_status()
         shard.profile = False
         if shard.transport == "peer":
@@ -799,7 +801,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: T={T_global} global tokens, {rec['E_local']} local experts/GPU of 256, "
                                    f"hidden 7168, intermediate 2048, top-8, {'skewed' if skew else 'N(0,1)'} router logits",
-                       "parallelism": f"ep{world}", "ep_transport": rec.get("ep_transport"), "l2": "inputs_exceed_l2 (expert weights >> 126 MB)",
+                       "parallelism": f"ep{world}", "ep_transport": rec.get("ep_transport"), "ep_partial_rows": rec.get("ep_partial_rows"), "l2": "inputs_exceed_l2 (expert weights >> 126 MB)",
                        "pairs_rank0": rec["pairs"], "active_experts_rank0": rec["active_experts"]},
             "e2e": rec["e2e"], "gpu_launches": rec["launches_per_step"] * rec["steps"],
             "clocks": rec.get("clocks"), "roofline": roof, "stage_us": {k: round(v, 1) for k, v in rec["stage_us"].items()},

@@ -27,6 +27,10 @@ PROLOGUE_MAX_T = 32
 SKINNY_MAX_T = 112
 
 
+PARTIAL_F32, PARTIAL_HALF = 0, 1      # b200moe_problem.partial_format
+HALF_ROW_BYTES = 15232                # bytes of one row in the half form
+
+
 class Problem(C.Structure):
     """Mirror of ``b200moe_problem``."""
 
@@ -55,6 +59,7 @@ class Problem(C.Structure):
         ("out_seg_start", C.c_int32 * 9),
         ("out_seg_base", C.c_void_p * 8),
         ("plan", C.c_void_p),
+        ("partial_format", C.c_int32),
     ]
 
 
@@ -70,6 +75,7 @@ class EpPeers(C.Structure):
         ("back_rows", C.c_void_p * 8),
         ("cap_recv", C.c_int32),
         ("cap_back", C.c_int32),
+        ("back_row_bytes", C.c_int32),
     ]
 
 
@@ -158,6 +164,7 @@ SYMBOLS = {
                                                                    C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)),
     "b200moe_set_wait_limit_cycles": (C.c_int, (C.c_int64,)),
     "b200moe_ep_combine": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
+    "b200moe_ep_combine_half": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p)),
     "b200moe_read_status": (C.c_int, (C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_int32 * 4))),
 }
 

@@ -323,6 +323,7 @@ int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* 
       ((!p->output && !p->output_f32) || !aligned16(p->output) || !aligned16(p->output_f32)))
     return B200MOE_EINVAL;
   if (p->out_seg_count < 0 || p->out_seg_count > 8) return B200MOE_EINVAL;
+  if (p->partial_format != B200MOE_PARTIAL_F32 && p->partial_format != B200MOE_PARTIAL_HALF) return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
   return launch_reduce(p, ws, static_cast<cudaStream_t>(stream));
@@ -346,6 +347,7 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
     return B200MOE_EINVAL;
   }
   if (p->out_seg_count < 0 || p->out_seg_count > 8) return B200MOE_EINVAL;
+  if (p->partial_format != B200MOE_PARTIAL_F32 && p->partial_format != B200MOE_PARTIAL_HALF) return B200MOE_EINVAL;
   for (int i = 0; i < p->out_seg_count; ++i)
     if (!p->out_seg_base[i] || !aligned16(p->out_seg_base[i]) || p->out_seg_start[i] > p->out_seg_start[i + 1])
       return B200MOE_EINVAL;

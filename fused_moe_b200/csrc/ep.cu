@@ -18,6 +18,7 @@ constexpr int ST_BAD_ADDRESS = 4;     // a kernel found a misaligned or out-of-r
 
 int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* counts, cudaStream_t st);
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st);
+int launch_combine_half(const void* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st);
 
 // chunk_bits over destination ranks: one warp per 32-token chunk, lane = token.
 __global__ void __launch_bounds__(128)
@@ -232,8 +233,8 @@ struct ExchangeTargets {
 };
 __global__ void __launch_bounds__(64)
 k_ep_exchange(const ExchangeTargets tg, const int* __restrict__ send_counts, int world, int rank, int epoch,
-              int cap_recv, int cap_back, long long limit_cycles, b200moe_ep_plan* __restrict__ plan,
-              int* __restrict__ status) {
+              int cap_recv, int cap_back, int back_row_floats, long long limit_cycles,
+              b200moe_ep_plan* __restrict__ plan, int* __restrict__ status) {
   __shared__ int s_timeout;
   pdl_launch_dependents();
   pdl_wait();
@@ -310,7 +311,7 @@ k_ep_exchange(const ExchangeTargets tg, const int* __restrict__ send_counts, int
         if (d < rank) before_me += ok ? mm[s][d] : 0;
         plan->matrix[s * 8 + d] = ok ? mm[s][d] : 0;
       }
-      plan->seg_base[s] = (s < world) ? tg.back[s] + static_cast<size_t>(before_me) * H : nullptr;
+      plan->seg_base[s] = (s < world) ? tg.back[s] + static_cast<size_t>(before_me) * back_row_floats : nullptr;
       if (ok && s < world) n_recv += mm[s][rank];
     }
     plan->seg_start[8] = n_recv;
@@ -457,7 +458,8 @@ int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, 
 int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers, const int32_t* send_counts, int32_t epoch,
                                b200moe_ep_plan* plan, int32_t* status, void* stream) {
   if (!peers || !send_counts || !plan || !status || peers->world < 1 || peers->world > 8 || peers->rank < 0 ||
-      peers->rank >= peers->world || peers->cap_recv < 0 || peers->cap_back < 0)
+      peers->rank >= peers->world || peers->cap_recv < 0 || peers->cap_back < 0 ||
+      (peers->back_row_bytes != 0 && peers->back_row_bytes != H * 4 && peers->back_row_bytes != B200MOE_HALF_ROW_BYTES))
     return B200MOE_EINVAL;
   if (reinterpret_cast<uintptr_t>(plan) & 7u) return B200MOE_EINVAL;
   ExchangeTargets tg = {};
@@ -470,7 +472,8 @@ int b200moe_ep_exchange_counts(const b200moe_ep_peers* peers, const int32_t* sen
     tg.back[d] = peers->back_rows[d];
   }
   B200MOE_CUDA_TRY(launch_pdl(k_ep_exchange, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream), tg, send_counts,
-                              peers->world, peers->rank, epoch, peers->cap_recv, peers->cap_back, g_wait_limit_cycles,
+                              peers->world, peers->rank, epoch, peers->cap_recv, peers->cap_back,
+                              (peers->back_row_bytes ? peers->back_row_bytes : H * 4) / 4, g_wait_limit_cycles,
                               plan, status));
   return B200MOE_OK;
 }
@@ -518,6 +521,16 @@ int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int3
   if ((reinterpret_cast<uintptr_t>(returned_rows) & 15u) || (reinterpret_cast<uintptr_t>(output) & 15u))
     return B200MOE_EINVAL;
   return launch_reduce_rows(returned_rows, slot_map, T, output, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_combine_half(const void* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output,
+                            void* stream) {
+  if (T < 0) return B200MOE_EINVAL;
+  if (T == 0) return B200MOE_OK;
+  if (!returned_rows || !slot_map || !output) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(returned_rows) & 15u) || (reinterpret_cast<uintptr_t>(output) & 15u))
+    return B200MOE_EINVAL;
+  return launch_combine_half(returned_rows, slot_map, T, output, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

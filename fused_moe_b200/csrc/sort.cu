@@ -9,6 +9,7 @@
 // A token selects an expert at most once, so the rank of pair (t, e) inside expert e is the number of earlier
 // tokens that selected e.  chunk_bits[c][e] holds that selection as one bit per token of 32-token chunk c; the rank
 // is chunk_base[c][e] + popc(bits & lanes_below).
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace b200moe {
@@ -195,12 +196,48 @@ struct OutSegments {
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
 // Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
 // (the expert-parallel combine adds rows that are already weighted).
+// Half rows (B200MOE_PARTIAL_HALF): eight consecutive columns = eight float16 with one shared power-of-two scale.
+constexpr int HALF_ROW_BYTES = B200MOE_HALF_ROW_BYTES;
+constexpr int HALF_ROW_SCALES = H * 2;            // byte offset of the 896 scale bytes
+static_assert(HALF_ROW_BYTES == H * 2 + H / 8 && HALF_ROW_BYTES % 16 == 0, "half-row layout");
+__device__ __forceinline__ void store_half_group(uint8_t* row, int v, const float (&acc)[8]) {
+  float m = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(acc[j]));
+  uint32_t eb = __float_as_uint(m) >> 23;          // biased exponent of the largest magnitude (sign bit is clear)
+  eb = eb < 14u ? 14u : (eb > 254u ? 254u : eb);   // 2^(141 - eb) must be a normal float; inf/nan stay inf/nan
+  const float k = __uint_as_float((268u - eb) << 23);
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __half2 h = __floats2half2_rn(acc[2 * j] * k, acc[2 * j + 1] * k);
+    o[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  reinterpret_cast<uint4*>(row)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  row[HALF_ROW_SCALES + v] = static_cast<uint8_t>(eb);
+}
+__device__ __forceinline__ void add_half_group(const uint8_t* row, int v, float (&acc)[8]) {
+  const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + v);
+  const uint32_t eb = __ldg(row + HALF_ROW_SCALES + v);
+  const float k = __uint_as_float((eb - 14u) << 23);   // 2^(eb - 141); eb = 14 decodes to zero
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    acc[2 * j] = fmaf(f.x, k, acc[2 * j]);
+    acc[2 * j + 1] = fmaf(f.y, k, acc[2 * j + 1]);
+  }
+}
+
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
          long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
-         const b200moe_ep_plan* __restrict__ plan, int* __restrict__ status, int* __restrict__ status_mirror) {
+         const b200moe_ep_plan* __restrict__ plan, int* __restrict__ status, int* __restrict__ status_mirror,
+         int half_rows) {
   int t = blockIdx.x;
-  float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr;
+  // un-rounded rows: float32 [7168] or the half form; either way `pitch` floats apart
+  const size_t pitch = half_rows ? HALF_ROW_BYTES / 4 : H;
+  float* dst_row = out_f32 ? out_f32 + static_cast<size_t>(t) * pitch : nullptr;
   if (segs.count > 0) {
     // rows of segment i go to segs.base[i], which may be memory of another GPU (plain 16-byte stores)
     int i = 0;
@@ -208,7 +245,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
     for (int j = 1; j < 8; ++j)
       if (j < segs.count && t >= segs.start[j]) i = j;
     out = nullptr;
-    dst_row = segs.base[i] + static_cast<size_t>(t - segs.start[i]) * H;
+    dst_row = segs.base[i] + static_cast<size_t>(t - segs.start[i]) * pitch;
   }
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
@@ -237,7 +274,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
     for (int j = 1; j < 8; ++j)
       if (j < plan->seg_count && t >= plan->seg_start[j]) i = j;
     out = nullptr;
-    dst_row = plan->seg_base[i] + static_cast<size_t>(t - plan->seg_start[i]) * H;
+    dst_row = plan->seg_base[i] + static_cast<size_t>(t - plan->seg_start[i]) * pitch;
     if (reinterpret_cast<uintptr_t>(dst_row) & 15u) {
       // never store through an address that does not add up: record it (status code 4) and skip the row
       if (status && threadIdx.x == 0 && atomicCAS(status, 0, 4) == 0) {
@@ -281,13 +318,46 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       }
       reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    if (dst_row) {
+    if (dst_row && half_rows) {
+      store_half_group(reinterpret_cast<uint8_t*>(dst_row), v, acc);
+    } else if (dst_row) {
       float4* dst = reinterpret_cast<float4*>(dst_row) + 2 * v;
       dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
       dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
   if (segs.count > 0 || plan) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
+}
+
+// out[t, :] = bf16(sum over the token's returned half rows, in slot order): the expert-parallel combine when the
+// partial rows travelled in the half form.  Same work split as k_reduce.
+__global__ void __launch_bounds__(128)
+k_combine_half(const uint8_t* __restrict__ rows, const int* __restrict__ slot_map, int T, uint16_t* __restrict__ out) {
+  const int t = blockIdx.x;
+  __shared__ int s_pos[TOP_K];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x < TOP_K) s_pos[threadIdx.x] = __ldg(slot_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
+  __syncthreads();
+  const int per = (H / 8) / gridDim.y;
+  for (int v = blockIdx.y * per + threadIdx.x; v < (blockIdx.y + 1) * per; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < TOP_K; ++k) {
+      const int pos = s_pos[k];
+      if (pos < 0) continue;
+      add_half_group(rows + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, acc);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      o[j] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
 }
 
 // CTAs per token of k_reduce: 7 x 128 threads = one vector per thread while the batch alone cannot fill the GPU
@@ -304,7 +374,12 @@ int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* 
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
                               static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none,
                               static_cast<const b200moe_ep_plan*>(nullptr), static_cast<int*>(nullptr),
-                              static_cast<int*>(nullptr)));
+                              static_cast<int*>(nullptr), 0));
+  return B200MOE_OK;
+}
+int launch_combine_half(const void* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
+  B200MOE_CUDA_TRY(launch_pdl(k_combine_half, dim3(T, reduce_splits(T)), dim3(128), 0, st,
+                              static_cast<const uint8_t*>(rows), slot_map, T, out));
   return B200MOE_OK;
 }
 
@@ -361,7 +436,7 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
                               p->output, p->output_f32, segs, p->plan, ws->status,
-                              ws->status_mirror));
+                              ws->status_mirror, p->partial_format == B200MOE_PARTIAL_HALF ? 1 : 0));
   return B200MOE_OK;
 }
 

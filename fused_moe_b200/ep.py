@@ -168,12 +168,19 @@ class CudaExpertParallelMoE:
     HDR_FLAGS, HDR_COUNTS, HDR_BYTES = 0, 256, 1024
 
     def __init__(self, weights: dict, rank: int, world: int, group=None, transport: str = "auto",
-                 max_tokens_per_rank: Optional[int] = None):
+                 max_tokens_per_rank: Optional[int] = None, partial_rows: Optional[str] = None):
         if E_GLOBAL % world:
             raise ValueError(f"world size {world} does not divide {E_GLOBAL} experts")
         if transport not in ("auto", "peer", "nccl"):
             raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
+        if partial_rows not in (None, "float", "half"):
+            raise ValueError("partial_rows must be 'float', 'half' or None")
         self.weights, self.rank, self.world, self.group = weights, rank, world, group
+        # Form of the partial rows a shard returns to the tokens' home ranks: float32 (28672 bytes per row) or the
+        # half form of b200moe_problem.partial_format (15232 bytes: eight float16 per power-of-two scale byte).  The
+        # return is the larger of the two exchanges of a step and is bound by NVLink, so more than one rank defaults
+        # to the half form (every rank must choose the same); a single rank sends nothing and keeps float32.
+        self.half_rows = (partial_rows == "half") if partial_rows is not None else world > 1
         # more than 8 ranks span several nodes: collectives only; one rank needs no transport at all, "auto" then takes
         # the shorter collective-free nccl branch and an explicit "peer" runs the peer protocol on a local slab
         self.transport = "nccl" if (world > 8 or (world == 1 and transport == "auto")) else transport
@@ -255,7 +262,8 @@ class CudaExpertParallelMoE:
         cap_back = T_cap * min(TOP_K, self.world)          # one returned row per (token, destination)
         off_recv = self.HDR_BYTES
         off_back = off_recv + (cap_recv * ROW_BYTES + 255) // 256 * 256
-        total = off_back + cap_back * H * 4
+        back_row_bytes = _lib.HALF_ROW_BYTES if self.half_rows else H * 4
+        total = off_back + cap_back * back_row_bytes
         slab, err, hdl = None, None, None
         if self.world == 1:
             slab = torch.empty(total, dtype=torch.uint8, device=device)   # the only "peer" is this rank itself
@@ -276,6 +284,7 @@ class CudaExpertParallelMoE:
             ptrs = [int(p) for p in hdl.buffer_ptrs]
         peers = _lib.EpPeers()
         peers.world, peers.rank, peers.cap_recv, peers.cap_back = self.world, self.rank, cap_recv, cap_back
+        peers.back_row_bytes = back_row_bytes
         for r in range(self.world):
             peers.flags[r] = ptrs[r] + self.HDR_FLAGS
             peers.counts[r] = ptrs[r] + self.HDR_COUNTS
@@ -419,10 +428,10 @@ class CudaExpertParallelMoE:
         self._mark("all_to_all_records")
         wts = self.weights
         part = K.kernel_from_records(recv, wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
-                                     wts["gemm2_weights_scale"], self.local_expert_offset)
+                                     wts["gemm2_weights_scale"], self.local_expert_offset, half_rows=self.half_rows)
         self._mark("local_experts")
         if self.world > 1:
-            back = torch.empty((n_send, H), dtype=torch.float32, device=device)
+            back = torch.empty((n_send,) + tuple(part.shape[1:]), dtype=part.dtype, device=device)
             dist.all_to_all_single(back, part, send_splits, recv_splits, group=self.group)
         else:
             back = part
@@ -433,8 +442,9 @@ class CudaExpertParallelMoE:
                 if n_send == 0:
                     output.zero_()
                 else:
-                    _lib.check(lib.b200moe_ep_combine(back.data_ptr(), b["slot_map"].data_ptr(), T, output.data_ptr(),
-                                                      stream), "b200moe_ep_combine")
+                    combine = lib.b200moe_ep_combine_half if self.half_rows else lib.b200moe_ep_combine
+                    _lib.check(combine(back.data_ptr(), b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
+                               "b200moe_ep_combine")
         self._mark("combine")
         return output
 
@@ -500,13 +510,15 @@ class CudaExpertParallelMoE:
             self._mark("records_to_peers")
             wts = self.weights
             K.kernel_from_records(pr["recv"], wts["gemm1_weights"], wts["gemm1_weights_scale"], wts["gemm2_weights"],
-                                  wts["gemm2_weights_scale"], self.local_expert_offset, plan=plan)
+                                  wts["gemm2_weights_scale"], self.local_expert_offset, plan=plan,
+                                  half_rows=self.half_rows)
             self._mark("local_experts_and_rows_to_peers")
             self._barrier(stream)
             self._mark("barrier")
             if T > 0:
                 back_ptr = pr["ptrs"][self.rank] + pr["off_back"]
-                _lib.check(lib.b200moe_ep_combine(back_ptr, b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
+                combine = lib.b200moe_ep_combine_half if self.half_rows else lib.b200moe_ep_combine
+                _lib.check(combine(back_ptr, b["slot_map"].data_ptr(), T, output.data_ptr(), stream),
                            "b200moe_ep_combine")
             self._mark("combine")
             # the status word follows the step to pinned host memory; the next call looks at it before it starts
@@ -515,6 +527,8 @@ class CudaExpertParallelMoE:
 
 
 def make_cuda_shard(weights: dict, rank: int, world: int, group=None, transport: str = "auto",
-                    max_tokens_per_rank: Optional[int] = None) -> CudaExpertParallelMoE:
-    """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts)."""
-    return CudaExpertParallelMoE(weights, rank, world, group, transport, max_tokens_per_rank)
+                    max_tokens_per_rank: Optional[int] = None,
+                    partial_rows: Optional[str] = None) -> CudaExpertParallelMoE:
+    """Shard backed by libb200moe.so: ``weights`` holds this rank's gemm1/gemm2 weights and scales (E_l experts);
+    ``partial_rows`` = "float" | "half" | None (half when world > 1) is the form in which partial rows return."""
+    return CudaExpertParallelMoE(weights, rank, world, group, transport, max_tokens_per_rank, partial_rows)

@@ -431,7 +431,7 @@ def kernel_from_topk(topk_idx, topk_weights, hidden_states, hidden_states_scale,
 
 @torch.no_grad()
 def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
-                        local_expert_offset, output=None, out_segments=None, plan=None):
+                        local_expert_offset, output=None, out_segments=None, plan=None, half_rows=False):
     """The layer over expert-parallel dispatch records read in place: ``records`` is uint8 [n, 7456] in the layout of
     ``b200moe_ep_dispatch`` (activations | 56 scales | 8 expert ids | 8 weights per row).  Returns float32 [n, 7168]
     partial rows (sum over THIS shard's experts), in record order.  With ``out_segments = (starts, bases)`` — row
@@ -439,7 +439,9 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
     memory) — the rows are stored there instead and nothing is returned.  With ``plan`` (device address of a
     ``b200moe_ep_plan`` filled by ``b200moe_ep_exchange_counts``) ``records`` is the whole receive buffer (its row
     count is a capacity): how many leading rows are real and where their partial rows go is read on the device, so the
-    host never learns the count; nothing is returned.  No reference counterpart."""
+    host never learns the count; nothing is returned.  With ``half_rows`` the partial rows are written in the half
+    form of ``b200moe_problem.partial_format`` (15232 bytes per row: eight float16 per scale byte) and the returned
+    tensor is uint8 [n, 15232]; segment and plan destinations then have that row pitch.  No reference counterpart."""
     if not torch.is_tensor(records) or records.dim() != 2 or records.shape[1] != _lib.EP_RECORD_BYTES:
         raise ValueError(f"records must be uint8 [n, {_lib.EP_RECORD_BYTES}]")
     if records.dtype != torch.uint8 or not records.is_contiguous():
@@ -462,7 +464,12 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
             raise ValueError("out_segments must cover rows 0..n with at most 8 segments")
         output = None
     elif output is None:
-        output = torch.empty((n, H), dtype=torch.float32, device=device)
+        output = (torch.empty((n, _lib.HALF_ROW_BYTES), dtype=torch.uint8, device=device) if half_rows
+                  else torch.empty((n, H), dtype=torch.float32, device=device))
+    elif half_rows:
+        if (output.dtype != torch.uint8 or tuple(output.shape) != (n, _lib.HALF_ROW_BYTES)
+                or not output.is_contiguous()):
+            raise ValueError("output must be a contiguous uint8 tensor of shape [n, 15232]")
     elif output.dtype != torch.float32 or tuple(output.shape) != (n, H) or not output.is_contiguous():
         raise ValueError("output must be a contiguous float32 tensor of shape [n, 7168]")
     if n == 0:
@@ -476,6 +483,7 @@ def kernel_from_records(records, gemm1_weights, gemm1_weights_scale, gemm2_weigh
         p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
         p.gemm1_weights, p.gemm1_weights_scale = w13.data_ptr(), w13s.data_ptr()
         p.gemm2_weights, p.gemm2_weights_scale = w2.data_ptr(), w2s.data_ptr()
+        p.partial_format = _lib.PARTIAL_HALF if half_rows else _lib.PARTIAL_F32
         if plan is not None:
             p.output, p.output_f32, p.plan = None, None, int(plan)
         elif out_segments is None:

@@ -111,7 +111,20 @@ typedef struct b200moe_problem {
    * are ignored.  This is what lets a rank launch the layer on received records without reading their count back to
    * the host. */
   const struct b200moe_ep_plan* plan;
+  /* Form of the un-rounded result rows (`output_f32`, out_seg_base[], plan->seg_base[]; `output` is always bfloat16):
+   *   B200MOE_PARTIAL_F32  (0)  7168 float32 per row, 28672 bytes;
+   *   B200MOE_PARTIAL_HALF (1)  15232 bytes per row: 896 groups of eight consecutive columns as eight float16 that
+   *     share one power-of-two scale (14336 bytes), then the 896 scale bytes.  Group g, scale byte b: column 8g + j =
+   *     half[8g + j] * 2^(b - 141); b is the biased float32 exponent of the group's largest magnitude (at least 14),
+   *     so that magnitude lands in [2^14, 2^15) and every value keeps 11 significant bits relative to it.
+   * In the second form the float* bases above are byte addresses of rows with a 15232-byte pitch.  It halves what an
+   * expert-parallel shard returns over NVLink; the sum of up to eight such rows per token (b200moe_ep_combine_half)
+   * stays within the bfloat16 rounding of the result.  The reference has no counterpart. */
+  int32_t partial_format;
 } b200moe_problem;
+#define B200MOE_PARTIAL_F32 0
+#define B200MOE_PARTIAL_HALF 1
+#define B200MOE_HALF_ROW_BYTES 15232
 
 /* Typed view of the caller-owned workspace.  R_max = (8*T/128 + E_local) * 128 rows bounds the padded sorted rows.
  * Integer metadata follows the reference's sort kernel (solution/python/pure_triton_impl.py:474-551):
@@ -287,6 +300,8 @@ typedef struct b200moe_ep_peers {
   float* back_rows[8];   /* rank r's buffer for the float32 partial rows returning to it, [cap_back, 7168] */
   int32_t cap_recv;      /* records every receive buffer holds */
   int32_t cap_back;      /* rows every return buffer holds */
+  int32_t back_row_bytes; /* pitch of the return buffers' rows: 0 or 28672 = float32 rows, 15232 = half rows
+                             (b200moe_problem.partial_format of the layer call that writes them must match) */
 } b200moe_ep_peers;
 /* What one rank needs to know about a step's traffic, computed ON THE DEVICE by b200moe_ep_exchange_counts and read
  * there by the kernels that follow (pack, the layer on the received records, the return of partial rows), so that no
@@ -328,6 +343,10 @@ int b200moe_ep_pack_peers_planned(const int32_t* topk_idx, const float* topk_w, 
  * quickly; a deployment can use it to bound how long a lost peer stalls a step. */
 int b200moe_set_wait_limit_cycles(int64_t cycles);
 int b200moe_ep_combine(const float* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output, void* stream);
+/* The same sum over returned rows in the B200MOE_PARTIAL_HALF form (15232-byte pitch): rows are decoded to float32,
+ * added in slot order and rounded to bfloat16 once. */
+int b200moe_ep_combine_half(const void* returned_rows, const int32_t* slot_map, int32_t T, uint16_t* output,
+                            void* stream);
 
 /* Synchronises `stream`, copies the device status word to *status (host) and clears it.
  * Returns B200MOE_EDEVICE if it was non-zero.  No reference counterpart (the reference has no device-side waits). */

@@ -306,6 +306,38 @@ def _world1_weights(inp):
     return dict(gemm1_weights=w13, gemm1_weights_scale=w13s, gemm2_weights=w2, gemm2_weights_scale=w2s)
 
 
+def test_expert_parallel_half_rows_world1(moe):
+    """Partial rows in the half form through both transports with one rank: the two transports give the same bits (same
+    kernels encode and decode), and the result is kernel()'s within the layer's tolerance — a token's row passes
+    through float16 with 11 significant bits once before the final bfloat16 rounding."""
+    from fused_moe_b200 import ep, synth
+    inp = gpu_inputs(300, 32, 4, 64, True)
+    wts = _world1_weights(inp)
+    shards = {t: ep.make_cuda_shard(wts, rank=0, world=1, transport=t, max_tokens_per_rank=512, partial_rows="half")
+              for t in ("nccl", "peer")}
+    # batches above the token-minor GEMM limit, where the shard's 256-expert layer adds in kernel()'s order
+    for T, seed in ((300, 4), (150, 9), (412, 12)):
+        cur = synth.make_inputs(T, 32, seed=seed, local_expert_offset=64, skew=True, device="cuda", weights=inp)
+        want = moe.kernel(**cur).float()
+        got = {}
+        for t, shard in shards.items():
+            if t == "peer" and shard._peer is not None:
+                shard._peer["slab"][shard._peer["off_back"]:].fill_(0xFF)     # stale bytes in the return buffer
+            got[t] = shard.forward(cur["routing_logits"], cur["routing_bias"], cur["hidden_states"],
+                                   cur["hidden_states_scale"], cur["routed_scaling_factor"]).clone()
+            moe.check_status()
+            shard.check_status()
+        assert torch.equal(got["nccl"], got["peer"]), f"T={T}"
+        err = (got["peer"].float() - want).abs()
+        assert (err <= 1e-2 + 2e-2 * want.abs()).all(), f"T={T}"
+        # one extra rounding at 2^-11 of the value, then bfloat16: at most one bfloat16 step from kernel() (values
+        # below 2^-28 of their group's maximum lose bits: they only matter at the absolute level)
+        bad = err > want.abs() * 2.0 ** -7 + 1e-6
+        assert not bad.any(), (f"T={T}: {int(bad.sum())} values, e.g. got {got['peer'].float()[bad][:4].tolist()} "
+                               f"want {want[bad][:4].tolist()}")
+        assert (got["peer"].float() != want).float().mean().item() < 0.2
+
+
 @pytest.mark.parametrize("transport", ["nccl", "peer"])
 def test_expert_parallel_shard_world1(moe, transport):
     """The expert-parallel plumbing with one rank reproduces kernel() bit for bit.  "nccl": dispatch and combine are
@@ -431,6 +463,50 @@ def test_host_memory_entry_point_equals_device_call(moe, T, slices):
     assert got.is_pinned() and torch.equal(got, want) and torch.equal(again, want)
     with pytest.raises(RuntimeError):
         moe.kernel_host(**inp)    # device activations
+
+
+def decode_half_rows(rows: torch.Tensor) -> torch.Tensor:
+    """uint8 [n, 15232] in the half form of b200moe_problem.partial_format -> float32 [n, 7168]."""
+    n = rows.shape[0]
+    halves = rows[:, :14336].contiguous().view(torch.float16).view(n, 896, 8).float()
+    scale = torch.ldexp(torch.ones((), device=rows.device), rows[:, 14336:].to(torch.int32) - 141)
+    return (halves * scale.view(n, 896, 1)).view(n, 7168)
+
+
+@pytest.mark.parametrize("T", [40, 700])
+def test_half_partial_rows(moe, T):
+    """The half form of the un-rounded rows (eight float16 sharing a power-of-two scale byte): every value within
+    2^-11 of ITSELF of the float32 row the same call produces otherwise, all-zero groups stay zero, and the combine
+    kernel adds decoded rows in slot order with one rounding."""
+    from fused_moe_b200 import _lib, ep
+    inp = gpu_inputs(T, 32, 5, 64, True)
+    idx, w = moe.route(inp["routing_logits"], inp["routing_bias"], inp["routed_scaling_factor"])
+    recs = ep.pack_rows(torch.arange(T, device="cuda"), inp["hidden_states"], inp["hidden_states_scale"], idx, w)
+    args = [inp[k] for k in ("gemm1_weights", "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale")]
+    full = moe.kernel_from_records(recs, *args, 64)
+    half = moe.kernel_from_records(recs, *args, 64, half_rows=True)
+    moe.check_status()
+    assert half.dtype == torch.uint8 and tuple(half.shape) == (T, 15232)
+    dec = decode_half_rows(half)
+    gmax = full.view(T, 896, 8).abs().amax(dim=2, keepdim=True)
+    # float16 keeps its own exponent per value: 11 significant bits of every value down to 2^-28 of the group maximum
+    f3 = full.view(T, 896, 8)
+    assert ((dec.view(T, 896, 8) - f3).abs() <= f3.abs() * 2.0 ** -11 + gmax * 2.0 ** -39).all()
+    zero_groups = gmax.squeeze(2) == 0
+    assert (half[:, 14336:][zero_groups] == 14).all() and (dec.view(T, 896, 8)[zero_groups] == 0).all()
+    nz = ~zero_groups
+    exp_of_max = torch.frexp(gmax.squeeze(2)[nz])[1] - 1 + 127          # biased exponent of the group maximum
+    assert torch.equal(half[:, 14336:][nz].to(torch.int32), exp_of_max.to(torch.int32))
+    # combine: token t adds rows t, (t + 3) % T and one missing slot
+    slot = torch.full((T, 8), -1, dtype=torch.int32, device="cuda")
+    slot[:, 0] = torch.arange(T, device="cuda")
+    slot[:, 5] = (torch.arange(T, device="cuda") + 3) % T
+    out = torch.empty((T, 7168), dtype=torch.bfloat16, device="cuda")
+    lib = _lib.load()
+    _lib.check(lib.b200moe_ep_combine_half(half.data_ptr(), slot.data_ptr(), T, out.data_ptr(),
+                                           torch.cuda.current_stream().cuda_stream), "b200moe_ep_combine_half")
+    want = (dec + dec[(torch.arange(T, device="cuda") + 3) % T]).bfloat16()
+    assert torch.equal(out, want)
 
 
 def test_host_memory_calls_overlap_with_ready_events(moe):
