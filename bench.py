@@ -275,6 +275,9 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
         names = ("topk_bits" if records is not None else "route", "sort", "gather", "gemm1", "gemm2", "reduce")
     if records is None and T <= _lib.SKINNY_MAX_T:   # the GEMM kernels b200moe_forward uses at this batch size
         names = tuple(n + "_skinny" if n in ("gemm1", "gemm2") else n for n in names)
+    elif "gemv1" not in names and T > _lib.SKINNY_MAX_T:
+        # above the token-minor limit the call keeps the GEMM2 rows in the half form between GEMM2 and the reduce
+        names = tuple(n + "_half" if n in ("gemm2", "reduce") else n for n in names)
     for name in names:
         fn = getattr(lib, "b200moe_" + name)
         _lib.check(fn(C.byref(p), C.byref(ws.struct), stream), name)  # warm
@@ -285,7 +288,7 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
             fn(C.byref(p), C.byref(ws.struct), stream)
         e1.record()
         torch.cuda.synchronize()
-        res[name.replace("_skinny", "")] = e0.elapsed_time(e1) * 1e3 / reps
+        res[name.replace("_skinny", "").replace("_half", "")] = e0.elapsed_time(e1) * 1e3 / reps
     if "gemv1" in names:
         _lib.check(lib.b200moe_sort(C.byref(p), C.byref(ws.struct), stream), "sort")  # only for the pair statistics
         torch.cuda.synchronize()
@@ -313,12 +316,14 @@ def time_planned_reduce(K, shard, E_local, offset, reps=5):
     p.E_local, p.local_expert_offset, p.routed_scaling_factor = E_local, offset, 1.0
     p.plan = pr["plan"].data_ptr()
     p.partial_format = _lib.PARTIAL_HALF if shard.half_rows else _lib.PARTIAL_F32
+    # the step left its GEMM2 rows in the form b200moe_forward uses at this capacity
+    reduce = lib.b200moe_reduce_half if recv.shape[0] > _lib.SKINNY_MAX_T else lib.b200moe_reduce
     torch.cuda.synchronize()
     barrier(shard.world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        _lib.check(lib.b200moe_reduce(C.byref(p), C.byref(ws.struct), stream), "b200moe_reduce")
+        _lib.check(reduce(C.byref(p), C.byref(ws.struct), stream), "b200moe_reduce")
     e1.record()
     torch.cuda.synchronize()
     barrier(shard.world)

@@ -146,7 +146,9 @@ SYMBOLS = {
     "b200moe_gemm2_skinny": (C.c_int, _PW),
     "b200moe_gemm1": (C.c_int, _PW),
     "b200moe_gemm2": (C.c_int, _PW),
+    "b200moe_gemm2_half": (C.c_int, _PW),
     "b200moe_reduce": (C.c_int, _PW),
+    "b200moe_reduce_half": (C.c_int, _PW),
     "b200moe_gemv1": (C.c_int, _PW),
     "b200moe_gemv2": (C.c_int, _PW),
     "b200moe_sort_static": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32) + (C.c_void_p,) * 7),

@@ -14,7 +14,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200moe.so"
 SOURCES = ["api.cu", "routing.cu", "sort.cu", "gemm.cu", "gemm_skinny.cu", "quant.cu", "sort_static.cu", "ep.cu", "decode.cu"]
-HEADERS = [CSRC / "common.cuh", CSRC / "gemm_common.cuh", PKG_DIR.parent / "include" / "b200moe.h"]
+HEADERS = [CSRC / "common.cuh", CSRC / "gemm_common.cuh", CSRC / "half_rows.cuh", PKG_DIR.parent / "include" / "b200moe.h"]
 
 
 def _nvcc() -> str:

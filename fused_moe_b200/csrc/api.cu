@@ -21,11 +21,11 @@ int launch_small_prologue(const b200moe_problem*, const b200moe_workspace*, cuda
 int launch_sort(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
 int launch_gather(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemm1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
-int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
+int launch_gemm2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool half_out);
 int launch_quantize_act(const void*, int, void*, float*, int, cudaStream_t);
 int launch_gemm1_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool);
 int launch_gemm2_skinny(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t, bool);
-int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t);
+int launch_reduce(const b200moe_problem*, const b200moe_workspace*, cudaStream_t, bool half_src);
 int launch_gemv1(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 int launch_gemv2(const b200moe_problem*, const b200moe_workspace*, int, cudaStream_t);
 
@@ -262,14 +262,20 @@ int b200moe_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, void* s
   return launch_gemm1(p, ws, sms, static_cast<cudaStream_t>(stream));
 }
 
-int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+static int gemm2_stage(const b200moe_problem* p, const b200moe_workspace* ws, void* stream, bool half_out) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
   if (p->T > 0 && (!p->gemm2_weights || !p->gemm2_weights_scale || !aligned16(p->gemm2_weights)))
     return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
-  return launch_gemm2(p, ws, sms, static_cast<cudaStream_t>(stream));
+  return launch_gemm2(p, ws, sms, static_cast<cudaStream_t>(stream), half_out);
+}
+int b200moe_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  return gemm2_stage(p, ws, stream, false);
+}
+int b200moe_gemm2_half(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  return gemm2_stage(p, ws, stream, true);
 }
 
 int b200moe_gemm1_skinny(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
@@ -316,7 +322,7 @@ int b200moe_gemv2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
   return launch_gemv2(p, ws, sms, static_cast<cudaStream_t>(stream));
 }
 
-int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+static int reduce_stage(const b200moe_problem* p, const b200moe_workspace* ws, void* stream, bool half_src) {
   int rc = check_problem(p, ws);
   if (rc) return rc;
   if (p->T > 0 && p->out_seg_count == 0 && !p->plan &&
@@ -326,7 +332,14 @@ int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* 
   if (p->partial_format != B200MOE_PARTIAL_F32 && p->partial_format != B200MOE_PARTIAL_HALF) return B200MOE_EINVAL;
   int sms;
   if ((rc = device_info(&sms))) return rc;
-  return launch_reduce(p, ws, static_cast<cudaStream_t>(stream));
+  return launch_reduce(p, ws, static_cast<cudaStream_t>(stream), half_src);
+}
+
+int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  return reduce_stage(p, ws, stream, false);
+}
+int b200moe_reduce_half(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
+  return reduce_stage(p, ws, stream, true);
 }
 
 int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void* stream) {
@@ -381,11 +394,14 @@ int b200moe_forward(const b200moe_problem* p, const b200moe_workspace* ws, void*
   if (p->T <= B200MOE_SKINNY_MAX_T) {
     if ((rc = launch_gemm1_skinny(p, ws, sms, st, after_gather))) return rc;
     if ((rc = launch_gemm2_skinny(p, ws, sms, st, true))) return rc;
-  } else {
-    if ((rc = launch_gemm1(p, ws, sms, st))) return rc;
-    if ((rc = launch_gemm2(p, ws, sms, st))) return rc;
+    return launch_reduce(p, ws, st, false);
   }
-  return launch_reduce(p, ws, st);
+  if ((rc = launch_gemm1(p, ws, sms, st))) return rc;
+  // Between the tile GEMM2 and the reduce of one call the per-expert rows live in the half form (eight float16 per
+  // power-of-two scale byte): the two kernels are bound by writing and reading them.  (The stage entry points
+  // b200moe_gemm2 / b200moe_reduce keep float32 rows.)
+  if ((rc = launch_gemm2(p, ws, sms, st, true))) return rc;
+  return launch_reduce(p, ws, st, true);
 }
 
 int b200moe_read_status(const b200moe_workspace* ws, void* stream, int32_t status[4]) {

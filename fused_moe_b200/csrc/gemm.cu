@@ -44,6 +44,7 @@
 
 #include "common.cuh"
 #include "gemm_common.cuh"
+#include "half_rows.cuh"
 
 namespace b200moe {
 
@@ -379,6 +380,41 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           __syncwarp();
         }
         if (valid && h == 0) args.inter_scale[static_cast<size_t>(ti.nt) * args.R_max + row] = s;
+      } else if (args.out_half) {
+        // Rows in the half form: the thread's 128 columns are 16 groups of eight (one scale byte each).  Same staging
+        // as below, 32 columns = four groups = 64 bytes of float16 per row at a time.
+        uint32_t (*stg)[20] = reinterpret_cast<uint32_t (*)[20]>(aux->out_stage[warp]);
+        const int rows_valid = ti.cnt - ti.m_local * BLOCK_M - q * 32;
+        uint8_t* obase = reinterpret_cast<uint8_t*>(args.expert_out) +
+                         static_cast<size_t>(ti.mblk * BLOCK_M + q * 32) * HALF_ROW_BYTES;
+        const int g0 = ti.nt * (TILE_N / 8) + h * 16;   // this thread's first group within the row
+        const int rsub = lane >> 2, csub = (lane & 3) * 4;
+        uint32_t scale_bytes[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int g = piece * 4 + v;
+            const float x[8] = {ACC(8 * g), ACC(8 * g + 1), ACC(8 * g + 2), ACC(8 * g + 3),
+                                ACC(8 * g + 4), ACC(8 * g + 5), ACC(8 * g + 6), ACC(8 * g + 7)};
+            uint32_t eb;
+            *reinterpret_cast<uint4*>(&stg[lane][4 * v]) = encode_half_group(x, eb);
+            scale_bytes[piece] |= eb << (8 * v);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int r = rsub + 8 * j;
+            const uint4 val = *reinterpret_cast<const uint4*>(&stg[r][csub]);
+            if (r < rows_valid)
+              *reinterpret_cast<uint4*>(obase + static_cast<size_t>(r) * HALF_ROW_BYTES + (g0 + piece * 4) * 16 +
+                                        csub * 4) = val;
+          }
+          __syncwarp();
+        }
+        if (lane < rows_valid)
+          *reinterpret_cast<uint4*>(obase + static_cast<size_t>(lane) * HALF_ROW_BYTES + HALF_ROW_SCALES + g0) =
+              make_uint4(scale_bytes[0], scale_bytes[1], scale_bytes[2], scale_bytes[3]);
       } else {
         // Thread-per-row stores would touch 32 rows with 16 bytes each per instruction.  Instead each warp passes its
         // 32 x 128 block through shared memory 16 columns at a time and stores 64 contiguous bytes per row (8 rows per
@@ -454,7 +490,8 @@ int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, 
 }
 
 template <int MODE>
-static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
+static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st,
+                       bool half_out) {
   if (p->T == 0) return B200MOE_OK;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -477,6 +514,7 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
   a.tile_ctr = nullptr;
   a.weights = nullptr;
   a.early_weights = 0;
+  a.out_half = half_out ? 1 : 0;
   a.partial = nullptr;
   a.E_local = p->E_local;
   a.R_max = ws->R_max;
@@ -498,10 +536,10 @@ static int launch_gemm(const b200moe_problem* p, const b200moe_workspace* ws, in
 }
 
 int launch_gemm1(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
-  return launch_gemm<1>(p, ws, num_sms, st);
+  return launch_gemm<1>(p, ws, num_sms, st, false);
 }
-int launch_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st) {
-  return launch_gemm<2>(p, ws, num_sms, st);
+int launch_gemm2(const b200moe_problem* p, const b200moe_workspace* ws, int num_sms, cudaStream_t st, bool half_out) {
+  return launch_gemm<2>(p, ws, num_sms, st, half_out);
 }
 
 }  // namespace b200moe

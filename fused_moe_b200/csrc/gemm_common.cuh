@@ -23,6 +23,7 @@ struct GemmArgs {
   int R_max;
   int early_weights;         // token-minor kernels inside b200moe_forward: weight stream starts before the dependency
                              // wait, see gemm_skinny.cu
+  int out_half;              // tile GEMM2: expert_out rows in the half form (half_rows.cuh) instead of float32
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {

@@ -601,6 +601,7 @@ static int launch(const b200moe_problem* p, const b200moe_workspace* ws, int num
   a.tile_ctr = ws->gemm_tile_ctr;
   a.partial = ws->gemm_partial;
   a.early_weights = early ? 1 : 0;
+  a.out_half = 0;
   a.weights = static_cast<const uint8_t*>(MODE == 1 ? p->gemm1_weights : p->gemm2_weights);
   if (!a.tile_ctr || !a.partial) return B200MOE_EWORKSPACE;
   if (MODE == 1) {

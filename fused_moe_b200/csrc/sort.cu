@@ -9,8 +9,8 @@
 // A token selects an expert at most once, so the rank of pair (t, e) inside expert e is the number of earlier
 // tokens that selected e.  chunk_bits[c][e] holds that selection as one bit per token of 32-token chunk c; the rank
 // is chunk_base[c][e] + popc(bits & lanes_below).
-#include <cuda_fp16.h>
 #include "common.cuh"
+#include "half_rows.cuh"
 
 namespace b200moe {
 
@@ -196,44 +196,11 @@ struct OutSegments {
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
 // Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
 // (the expert-parallel combine adds rows that are already weighted).
-// Half rows (B200MOE_PARTIAL_HALF): eight consecutive columns = eight float16 with one shared power-of-two scale.
-constexpr int HALF_ROW_BYTES = B200MOE_HALF_ROW_BYTES;
-constexpr int HALF_ROW_SCALES = H * 2;            // byte offset of the 896 scale bytes
-static_assert(HALF_ROW_BYTES == H * 2 + H / 8 && HALF_ROW_BYTES % 16 == 0, "half-row layout");
-__device__ __forceinline__ void store_half_group(uint8_t* row, int v, const float (&acc)[8]) {
-  float m = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(acc[j]));
-  uint32_t eb = __float_as_uint(m) >> 23;          // biased exponent of the largest magnitude (sign bit is clear)
-  eb = eb < 14u ? 14u : (eb > 254u ? 254u : eb);   // 2^(141 - eb) must be a normal float; inf/nan stay inf/nan
-  const float k = __uint_as_float((268u - eb) << 23);
-  uint32_t o[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    __half2 h = __floats2half2_rn(acc[2 * j] * k, acc[2 * j + 1] * k);
-    o[j] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  reinterpret_cast<uint4*>(row)[v] = make_uint4(o[0], o[1], o[2], o[3]);
-  row[HALF_ROW_SCALES + v] = static_cast<uint8_t>(eb);
-}
-__device__ __forceinline__ void add_half_group(const uint8_t* row, int v, float (&acc)[8]) {
-  const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + v);
-  const uint32_t eb = __ldg(row + HALF_ROW_SCALES + v);
-  const float k = __uint_as_float((eb - 14u) << 23);   // 2^(eb - 141); eb = 14 decodes to zero
-  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-    acc[2 * j] = fmaf(f.x, k, acc[2 * j]);
-    acc[2 * j + 1] = fmaf(f.y, k, acc[2 * j + 1]);
-  }
-}
-
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
          long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
          const b200moe_ep_plan* __restrict__ plan, int* __restrict__ status, int* __restrict__ status_mirror,
-         int half_rows) {
+         int half_rows, int half_src) {
   int t = blockIdx.x;
   // un-rounded rows: float32 [7168] or the half form; either way `pitch` floats apart
   const size_t pitch = half_rows ? HALF_ROW_BYTES / 4 : H;
@@ -302,6 +269,10 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       int pos = s_pos[k];
       if (pos < 0) continue;
       float w = s_w[k];
+      if (half_src) {   // the tile GEMM2 of the same layer call left its rows in the half form (uniform branch)
+        fma_half_group(reinterpret_cast<const uint8_t*>(expert_out) + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, w, acc);
+        continue;
+      }
       const float4* src = reinterpret_cast<const float4*>(expert_out + static_cast<size_t>(pos) * H) + 2 * v;
       float4 a = __ldg(src), b = __ldg(src + 1);
       acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]);
@@ -348,7 +319,7 @@ k_combine_half(const uint8_t* __restrict__ rows, const int* __restrict__ slot_ma
     for (int k = 0; k < TOP_K; ++k) {
       const int pos = s_pos[k];
       if (pos < 0) continue;
-      add_half_group(rows + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, acc);
+      fma_half_group(rows + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, 1.0f, acc);
     }
     uint32_t o[4];
 #pragma unroll
@@ -374,7 +345,7 @@ int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* 
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
                               static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none,
                               static_cast<const b200moe_ep_plan*>(nullptr), static_cast<int*>(nullptr),
-                              static_cast<int*>(nullptr), 0));
+                              static_cast<int*>(nullptr), 0, 0));
   return B200MOE_OK;
 }
 int launch_combine_half(const void* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
@@ -426,7 +397,7 @@ int launch_gather(const b200moe_problem* p, const b200moe_workspace* ws, int num
   return B200MOE_OK;
 }
 
-int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st) {
+int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStream_t st, bool half_src) {
   if (p->T == 0) return B200MOE_OK;
   const float* w = p->routing_logits ? ws->topk_w : p->topk_w_in;
   OutSegments segs = {};
@@ -436,7 +407,8 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
                               p->output, p->output_f32, segs, p->plan, ws->status,
-                              ws->status_mirror, p->partial_format == B200MOE_PARTIAL_HALF ? 1 : 0));
+                              ws->status_mirror, p->partial_format == B200MOE_PARTIAL_HALF ? 1 : 0,
+                              half_src ? 1 : 0));
   return B200MOE_OK;
 }
 

@@ -246,6 +246,12 @@ int b200moe_gemv2(const b200moe_problem* p, const b200moe_workspace* ws, void* s
  * Replaces _token_reduce_kernel (solution/python/pure_triton_impl.py:1758-1821) and
  * _token_reduce_weighted_kernel (solution/python/triton_impl.py:163-207). */
 int b200moe_reduce(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+/* The pair b200moe_forward runs for batches above B200MOE_SKINNY_MAX_T: b200moe_gemm2 with its rows left in the
+ * workspace's expert_out array in the half form (see partial_format: 15232-byte pitch), and b200moe_reduce reading that
+ * form.  Both kernels are bound by those rows' bytes, which this halves; a value keeps 11 significant bits, the sum of
+ * eight is rounded to bfloat16.  Same reference kernels as the float32 pair above. */
+int b200moe_gemm2_half(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
+int b200moe_reduce_half(const b200moe_problem* p, const b200moe_workspace* ws, void* stream);
 
 /* Token sort for callers that cannot allocate device memory (a process that gave all of HBM to its own pool, a plugin
  * with a memory budget fixed at start-up, a region where allocation is forbidden).  Same results as b200moe_topk_bits

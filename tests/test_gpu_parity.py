@@ -238,6 +238,43 @@ def test_token_minor_gemms_match_tile_gemms(moe, T, E_local, seed, offset, skew)
         assert float((first - ref).abs().max()) <= tol
 
 
+def test_gemm2_rows_in_half_form(moe):
+    """b200moe_gemm2_half leaves the rows of b200moe_gemm2 in the half form (every value within 2^-11 of itself, rows of
+    pad tokens untouched), and b200moe_reduce_half over them gives the bytes of the whole call."""
+    from fused_moe_b200 import _lib
+    from fused_moe_b200.kernel import _problem
+    lib = _lib.load()
+    T, E_local = 700, 32
+    inp = gpu_inputs(T, E_local, 3, 32, True)
+    out = moe.kernel(**inp).clone()
+    torch.cuda.synchronize()
+    ws = moe.last_workspace()
+    R = ws.struct.R_max
+    stream = torch.cuda.current_stream().cuda_stream
+    again = torch.empty_like(out)
+    p = _problem(T, E_local, 32, float(inp["routed_scaling_factor"]), inp["routing_logits"], inp["routing_bias"],
+                 inp["hidden_states"], inp["hidden_states_scale"], inp["gemm1_weights"], inp["gemm1_weights_scale"],
+                 inp["gemm2_weights"], inp["gemm2_weights_scale"], again)
+    rows = int(ws.view("total_blocks", torch.int32, (1,)).item()) * 128
+    real = ws.view("sorted_token_ids", torch.int32, (R,))[:rows] < T
+    _lib.check(lib.b200moe_gemm2(C.byref(p), C.byref(ws.struct), stream), "gemm2")
+    torch.cuda.synchronize()
+    full = ws.view("expert_out", torch.float32, (R, 7168))[:rows].clone()
+    ws.view("expert_out", torch.uint8, (R * 7168 * 4,)).fill_(0x5A)
+    _lib.check(lib.b200moe_gemm2_half(C.byref(p), C.byref(ws.struct), stream), "gemm2_half")
+    torch.cuda.synchronize()
+    half = ws.view("expert_out", torch.uint8, (R * 7168 * 4,))[:rows * 15232].view(rows, 15232).clone()
+    dec = decode_half_rows(half[real])
+    f3 = full[real].view(-1, 896, 8)
+    gmax = f3.abs().amax(dim=2, keepdim=True)
+    assert ((dec.view(-1, 896, 8) - f3).abs() <= f3.abs() * 2.0 ** -11 + gmax * 2.0 ** -39).all()
+    assert (half[~real] == 0x5A).all()          # rows of pad tokens are not written
+    _lib.check(lib.b200moe_reduce_half(C.byref(p), C.byref(ws.struct), stream), "reduce_half")
+    torch.cuda.synchronize()
+    moe.check_status()
+    assert torch.equal(again, out)
+
+
 def test_from_topk_equals_routed(moe):
     """kernel_from_topk with the routing's own (ids, weights) reproduces kernel() bit for bit."""
     inp = gpu_inputs(80, 32, 1, 0, False)
@@ -469,7 +506,7 @@ def decode_half_rows(rows: torch.Tensor) -> torch.Tensor:
     """uint8 [n, 15232] in the half form of b200moe_problem.partial_format -> float32 [n, 7168]."""
     n = rows.shape[0]
     halves = rows[:, :14336].contiguous().view(torch.float16).view(n, 896, 8).float()
-    scale = torch.ldexp(torch.ones((), device=rows.device), rows[:, 14336:].to(torch.int32) - 141)
+    scale = torch.pow(2.0, rows[:, 14336:].to(torch.float32) - 141.0)
     return (halves * scale.view(n, 896, 1)).view(n, 7168)
 
 
