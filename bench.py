@@ -245,7 +245,7 @@ class _Null:
 
 
 def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
-    """CUDA-event duration (us) of each stage kernel, launched on its own through the stage entry points.  With
+    """CUDA-event duration (us) of each stage kernel, launched through the stage entry points in call order.  With
     `records` (expert-parallel receive buffer) the routing stage is replaced by the chunk-bits stage and the kernels
     read the records in place."""
     from fused_moe_b200 import _lib
@@ -278,17 +278,35 @@ def stage_times(K, inp, T, E_local, offset, reps=5, records=None):
     elif "gemv1" not in names and T > _lib.SKINNY_MAX_T:
         # above the token-minor limit the call keeps the GEMM2 rows in the half form between GEMM2 and the reduce
         names = tuple(n + "_half" if n in ("gemm2", "reduce") else n for n in names)
-    for name in names:
-        fn = getattr(lib, "b200moe_" + name)
+    # The stages run in the order of a layer call, `reps` calls back to back with an event between every two stages, so
+    # each kernel is timed under the clocks and the cache state it has inside a step (a loop over one kernel alone runs
+    # the GEMMs under a heavier power cap than the step does).
+    # (Small batches keep one loop per kernel: their kernels are shorter than the gap between two launches from Python,
+    # which an event between every two stages would measure instead.)
+    fns = [getattr(lib, "b200moe_" + name) for name in names]
+    for name, fn in zip(names, fns):
         _lib.check(fn(C.byref(p), C.byref(ws.struct), stream), name)  # warm
+    torch.cuda.synchronize()
+    if T >= 4096:
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(reps)]
+        for r in range(reps):
+            for i, fn in enumerate(fns):
+                marks[r][i].record()
+                fn(C.byref(p), C.byref(ws.struct), stream)
+            marks[r][len(names)].record()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn(C.byref(p), C.byref(ws.struct), stream)
-        e1.record()
-        torch.cuda.synchronize()
-        res[name.replace("_skinny", "").replace("_half", "")] = e0.elapsed_time(e1) * 1e3 / reps
+        for i, name in enumerate(names):
+            us = sum(marks[r][i].elapsed_time(marks[r][i + 1]) for r in range(reps)) * 1e3 / reps
+            res[name.replace("_skinny", "").replace("_half", "")] = us
+    else:
+        for name, fn in zip(names, fns):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn(C.byref(p), C.byref(ws.struct), stream)
+            e1.record()
+            torch.cuda.synchronize()
+            res[name.replace("_skinny", "").replace("_half", "")] = e0.elapsed_time(e1) * 1e3 / reps
     if "gemv1" in names:
         _lib.check(lib.b200moe_sort(C.byref(p), C.byref(ws.struct), stream), "sort")  # only for the pair statistics
         torch.cuda.synchronize()
