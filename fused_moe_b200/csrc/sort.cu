@@ -196,6 +196,10 @@ struct OutSegments {
 // out[t, :] = sum_k w[t,k] * expert_out[scatter_map[t,k], :] in fp32, k ascending; 16-byte loads and stores.
 // Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
 // (the expert-parallel combine adds rows that are already weighted).
+// G = groups of eight columns a thread takes per round: 4 when the source rows are in the half form and a CTA owns a
+// whole token (64 contiguous bytes of float16 and ONE 4-byte load for the four scale bytes per source row, instead
+// of a 16-byte and a 1-byte load per group), else 1.
+template <int G>
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
          long long w_stride, int T, uint16_t* __restrict__ out, float* __restrict__ out_f32, const OutSegments segs,
@@ -259,42 +263,67 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   __syncthreads();
   // gridDim.y CTAs share a token's 896 eight-column vectors (small batches: a token per CTA left most SMs idle and
   // made each thread walk seven dependent rounds of loads)
-  const int per = (H / 8) / gridDim.y;
-  for (int v = blockIdx.y * per + threadIdx.x; v < (blockIdx.y + 1) * per; v += blockDim.x) {
-    float acc[8];
+  const int per = (H / 8 / G) / gridDim.y;
+  for (int u = blockIdx.y * per + threadIdx.x; u < (blockIdx.y + 1) * per; u += blockDim.x) {
+    float acc[G][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < TOP_K; ++k) {
       int pos = s_pos[k];
       if (pos < 0) continue;
       float w = s_w[k];
-      if (half_src) {   // the tile GEMM2 of the same layer call left its rows in the half form (uniform branch)
-        fma_half_group(reinterpret_cast<const uint8_t*>(expert_out) + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, w, acc);
+      if (G > 1) {
+        // half-form source rows, four groups per thread (only launched with half_src)
+        const uint8_t* row = reinterpret_cast<const uint8_t*>(expert_out) + static_cast<size_t>(pos) * HALF_ROW_BYTES;
+        const uint32_t sc4 = __ldg(reinterpret_cast<const uint32_t*>(row + HALF_ROW_SCALES) + u);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + G * u + g);
+          const float kw = __uint_as_float((((sc4 >> (8 * g)) & 0xffu) - 14u) << 23) * w;
+          const uint32_t x[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x[j]));
+            acc[g][2 * j] = fmaf(f.x, kw, acc[g][2 * j]);
+            acc[g][2 * j + 1] = fmaf(f.y, kw, acc[g][2 * j + 1]);
+          }
+        }
         continue;
       }
-      const float4* src = reinterpret_cast<const float4*>(expert_out + static_cast<size_t>(pos) * H) + 2 * v;
-      float4 a = __ldg(src), b = __ldg(src + 1);
-      acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]);
-      acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
-      acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]);
-      acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
-    }
-    if (out) {
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-        o[j] = *reinterpret_cast<uint32_t*>(&b);
+      if (half_src) {   // the tile GEMM2 of the same layer call left its rows in the half form (uniform branch)
+        fma_half_group(reinterpret_cast<const uint8_t*>(expert_out) + static_cast<size_t>(pos) * HALF_ROW_BYTES, u, w,
+                       acc[0]);
+        continue;
       }
-      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      const float4* src = reinterpret_cast<const float4*>(expert_out + static_cast<size_t>(pos) * H) + 2 * u;
+      float4 a = __ldg(src), b = __ldg(src + 1);
+      acc[0][0] = fmaf(w, a.x, acc[0][0]); acc[0][1] = fmaf(w, a.y, acc[0][1]);
+      acc[0][2] = fmaf(w, a.z, acc[0][2]); acc[0][3] = fmaf(w, a.w, acc[0][3]);
+      acc[0][4] = fmaf(w, b.x, acc[0][4]); acc[0][5] = fmaf(w, b.y, acc[0][5]);
+      acc[0][6] = fmaf(w, b.z, acc[0][6]); acc[0][7] = fmaf(w, b.w, acc[0][7]);
     }
-    if (dst_row && half_rows) {
-      store_half_group(reinterpret_cast<uint8_t*>(dst_row), v, acc);
-    } else if (dst_row) {
-      float4* dst = reinterpret_cast<float4*>(dst_row) + 2 * v;
-      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int v = G * u + g;
+      if (out) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(acc[g][2 * j], acc[g][2 * j + 1]);
+          o[j] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      if (dst_row && half_rows) {
+        store_half_group(reinterpret_cast<uint8_t*>(dst_row), v, acc[g]);
+      } else if (dst_row) {
+        float4* dst = reinterpret_cast<float4*>(dst_row) + 2 * v;
+        dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+      }
     }
   }
   if (segs.count > 0 || plan) __threadfence_system();  // peer stores are visible system-wide before the barrier that follows
@@ -342,7 +371,7 @@ int launch_rank_scan(const uint32_t* bits, int n_chunks, int E, int* base, int* 
 }
 int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
   OutSegments none = {};
-  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
+  B200MOE_CUDA_TRY(launch_pdl(k_reduce<1>, dim3(T, reduce_splits(T)), dim3(128), 0, st, rows, slot_map, static_cast<const float*>(nullptr),
                               static_cast<long long>(TOP_K), T, out, static_cast<float*>(nullptr), none,
                               static_cast<const b200moe_ep_plan*>(nullptr), static_cast<int*>(nullptr),
                               static_cast<int*>(nullptr), 0, 0));
@@ -404,7 +433,9 @@ int launch_reduce(const b200moe_problem* p, const b200moe_workspace* ws, cudaStr
   segs.count = p->out_seg_count;
   for (int i = 0; i < 8; ++i) segs.base[i] = p->out_seg_base[i];
   for (int i = 0; i < 9; ++i) segs.start[i] = p->out_seg_start[i];
-  B200MOE_CUDA_TRY(launch_pdl(k_reduce, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
+  // half-form source rows and one CTA per token: four groups per thread (see k_reduce)
+  auto kern = (half_src && reduce_splits(p->T) == 1u) ? k_reduce<4> : k_reduce<1>;
+  B200MOE_CUDA_TRY(launch_pdl(kern, dim3(p->T, reduce_splits(p->T)), dim3(128), 0, st, ws->expert_out, ws->scatter_map, w,
                               (!p->routing_logits && p->topk_row_stride) ? p->topk_row_stride : static_cast<long long>(TOP_K), p->T,
                               p->output, p->output_f32, segs, p->plan, ws->status,
                               ws->status_mirror, p->partial_format == B200MOE_PARTIAL_HALF ? 1 : 0,
