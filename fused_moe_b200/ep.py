@@ -450,11 +450,13 @@ class CudaExpertParallelMoE:
 
     @torch.no_grad()
     def forward_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor,
-                     output: Optional[torch.Tensor] = None, slices: int = 2, ready_event=None) -> torch.Tensor:
+                     output: Optional[torch.Tensor] = None, slices: Optional[int] = None,
+                     ready_event=None) -> torch.Tensor:
         """``forward`` for a rank whose tokens live in HOST memory: ``routing_logits``, ``hidden_states``,
         ``hidden_states_scale`` and ``output`` are pinned host tensors (``output=None`` allocates one); the bias is a
         device tensor.  The rank's tokens are cut into ``slices`` equal runs and every run is one complete
-        expert-parallel step (so EVERY rank must pass the same ``slices``); the host-to-device copy of run i + 1 and the
+        expert-parallel step (so EVERY rank must pass the same ``slices``; default 2, or 1 with ``ready_event``, when
+        the overlap comes from the neighbouring calls); the host-to-device copy of run i + 1 and the
         device-to-host copy of run i - 1 go over two side streams and overlap the step on run i.  Rows are independent,
         so the result equals one ``forward`` on all tokens.  Returns ``output`` after queueing everything: the caller's
         current stream waits for the last copy, unless ``ready_event`` is given — then that event is recorded after the
@@ -469,6 +471,8 @@ class CudaExpertParallelMoE:
         device = routing_bias.device
         if output is None:
             output = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+        if slices is None:
+            slices = 1 if ready_event is not None else 2
         if slices < 1 or (T > 0 and slices > T):
             raise ValueError("slices must be in 1..T")
         if T == 0:
