@@ -472,7 +472,7 @@ class CudaExpertParallelMoE:
         if output is None:
             output = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
         if slices is None:
-            slices = 1 if ready_event is not None else 2
+            slices = 1 if (ready_event is not None or T < 2) else 2
         if slices < 1 or (T > 0 and slices > T):
             raise ValueError("slices must be in 1..T")
         if T == 0:
