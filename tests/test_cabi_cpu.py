@@ -154,12 +154,23 @@ def test_ctypes_mirrors_match_the_header_layout(tmp_path):
         lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
         for field, _ in mirror._fields_:
             lines.append(f'  printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    # the constants the package repeats on the Python side
+    consts = {"B200MOE_SORT_STATIC_MAX_ENTRIES": _lib.SORT_STATIC_MAX_ENTRIES, "B200MOE_EP_RECORD_BYTES": _lib.EP_RECORD_BYTES,
+              "B200MOE_DECODE_MAX_T": _lib.DECODE_MAX_T, "B200MOE_DECODE_MAX_WORK": _lib.DECODE_MAX_WORK,
+              "B200MOE_SKINNY_MAX_T": _lib.SKINNY_MAX_T, "B200MOE_PROLOGUE_MAX_T": _lib.PROLOGUE_MAX_T,
+              "B200MOE_PARTIAL_F32": _lib.PARTIAL_F32, "B200MOE_PARTIAL_HALF": _lib.PARTIAL_HALF,
+              "B200MOE_HALF_ROW_BYTES": _lib.HALF_ROW_BYTES}
+    for cname in consts:
+        lines.append(f'  printf("{cname} %d\\n", (int){cname});')
     lines += ['  return 0;', '}']
     src = tmp_path / "layout.c"
     src.write_text("\n".join(lines))
     exe = tmp_path / "layout"
     subprocess.run([cc, "-I", str(root / "include"), str(src), "-o", str(exe)], check=True)
     got = dict(l.split() for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, value in consts.items():
+        assert int(got[cname]) == value, cname
+    assert _lib.HALF_ROW_BYTES == 7168 * 2 + 7168 // 8
     for cname, mirror in pairs.items():
         assert int(got[cname]) == C.sizeof(mirror), cname
         for field, _ in mirror._fields_:
