@@ -9,7 +9,8 @@ The reference is single-GPU: its only hook for sharding is ``local_expert_offset
      every rank that owns at least one of its experts — group-limited routing bounds that by 4 ranks at G = 8;
   3. the receiver runs the layer on what arrived (``kernel_from_topk``: sort, gather, GEMM1+SwiGLU, GEMM2, reduce over
      ITS experts only), giving one partial row per received token, already weighted and summed over its experts;
-  4. combine: fp32 partial rows return to the token's home rank, which adds them and rounds once to bf16.
+  4. combine: un-rounded partial rows (float32, or eight float16 per power-of-two scale byte) return to the token's
+     home rank, which adds them and rounds once to bf16.
 
 Payloads cross NVLink/NVSwitch either as plain peer stores from the pack and reduce kernels or as NCCL collectives;
 either way they land in local HBM before any kernel reads them.  Two classes share
@@ -152,7 +153,7 @@ class CudaExpertParallelMoE:
     "peer" (default up to 8 GPUs of one node): one slab per rank — flags, count matrix, receive records, returned
     partial rows — is mapped into every rank (torch symmetric memory, plain peer mappings, no multicast).  A step is
     route -> rank -> count exchange + barrier -> pack (records stored straight into the destinations' slabs) -> barrier
-    -> the layer on the received records, its last kernel storing each fp32 partial row straight into the home rank's
+    -> the layer on the received records, its last kernel storing each partial row straight into the home rank's
     slab -> barrier -> combine.  The counts never reach the host: ``b200moe_ep_exchange_counts`` leaves a plan in device
     memory that the following kernels read, so a step has NO host synchronisation and no collective call.
 

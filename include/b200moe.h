@@ -303,7 +303,7 @@ typedef struct b200moe_ep_peers {
   int32_t* flags[8];
   /* used by b200moe_ep_exchange_counts only (may stay NULL / 0 otherwise): */
   int32_t* counts[8];    /* rank r's copy of the count matrix, int32 [8][8]: counts[r][s*8+d] = records s sends to d */
-  float* back_rows[8];   /* rank r's buffer for the float32 partial rows returning to it, [cap_back, 7168] */
+  float* back_rows[8];   /* rank r's buffer for the partial rows returning to it: cap_back rows of back_row_bytes */
   int32_t cap_recv;      /* records every receive buffer holds */
   int32_t cap_back;      /* rows every return buffer holds */
   int32_t back_row_bytes; /* pitch of the return buffers' rows: 0 or 28672 = float32 rows, 15232 = half rows
