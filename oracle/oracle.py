@@ -149,3 +149,33 @@ def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
 def sigmoid(x: np.ndarray) -> np.ndarray:
     lib = _load()
     return np.array([lib.oracle_sigmoid(float(v)) for v in np.asarray(x, dtype=np.float32).ravel()], dtype=np.float32)
+
+
+def encode_half_rows(x: np.ndarray) -> np.ndarray:
+    """float32 [n, 7168] -> uint8 [n, 15232]: the half form of un-rounded result rows that the library uses between
+    GEMM2 and the reduce and for the partial rows an expert-parallel shard returns (no reference counterpart; the
+    format is stated in include/b200moe.h at ``partial_format``).  Group g = columns 8g..8g+7: scale byte b = biased
+    float32 exponent of the group's largest magnitude, clamped to [14, 254]; the eight values times 2^(141 - b),
+    rounded to float16 (nearest even); 896 x 16 bytes of float16, then the 896 scale bytes."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[0]
+    g = x.reshape(n, 896, 8)
+    m = np.abs(g).max(axis=2)
+    eb = (m.view(np.uint32) >> 23).astype(np.int64)
+    eb = np.clip(eb, 14, 254)
+    k = ((268 - eb) << 23).astype(np.uint32).view(np.float32)           # 2^(141 - eb), exact
+    halves = (g * k[:, :, None]).astype(np.float16)                     # a power-of-two factor: the product is exact
+    out = np.empty((n, 15232), dtype=np.uint8)
+    out[:, :14336] = halves.reshape(n, 7168).view(np.uint8).reshape(n, 14336)
+    out[:, 14336:] = eb.astype(np.uint8)
+    return out
+
+
+def decode_half_rows(rows: np.ndarray) -> np.ndarray:
+    """uint8 [n, 15232] -> float32 [n, 7168]: value = float16 * 2^(b - 141) (b = 14 decodes to zero)."""
+    rows = np.ascontiguousarray(rows, dtype=np.uint8)
+    n = rows.shape[0]
+    halves = rows[:, :14336].copy().view(np.float16).reshape(n, 896, 8).astype(np.float32)
+    eb = rows[:, 14336:].astype(np.int64)
+    k = ((eb - 14) << 23).astype(np.uint32).view(np.float32)
+    return (halves * k[:, :, None]).reshape(n, 7168)

@@ -238,7 +238,7 @@ def test_token_minor_gemms_match_tile_gemms(moe, T, E_local, seed, offset, skew)
         assert float((first - ref).abs().max()) <= tol
 
 
-def test_gemm2_rows_in_half_form(moe):
+def test_gemm2_rows_in_half_form(moe, oracle):
     """b200moe_gemm2_half leaves the rows of b200moe_gemm2 in the half form (every value within 2^-11 of itself, rows of
     pad tokens untouched), and b200moe_reduce_half over them gives the bytes of the whole call."""
     from fused_moe_b200 import _lib
@@ -264,6 +264,7 @@ def test_gemm2_rows_in_half_form(moe):
     _lib.check(lib.b200moe_gemm2_half(C.byref(p), C.byref(ws.struct), stream), "gemm2_half")
     torch.cuda.synchronize()
     half = ws.view("expert_out", torch.uint8, (R * 7168 * 4,))[:rows * 15232].view(rows, 15232).clone()
+    assert np.array_equal(half[real].cpu().numpy(), oracle.encode_half_rows(full[real].cpu().numpy()))
     dec = decode_half_rows(half[real])
     f3 = full[real].view(-1, 896, 8)
     gmax = f3.abs().amax(dim=2, keepdim=True)
@@ -511,7 +512,7 @@ def decode_half_rows(rows: torch.Tensor) -> torch.Tensor:
 
 
 @pytest.mark.parametrize("T", [40, 700])
-def test_half_partial_rows(moe, T):
+def test_half_partial_rows(moe, oracle, T):
     """The half form of the un-rounded rows (eight float16 sharing a power-of-two scale byte): every value within
     2^-11 of ITSELF of the float32 row the same call produces otherwise, all-zero groups stay zero, and the combine
     kernel adds decoded rows in slot order with one rounding."""
@@ -524,6 +525,8 @@ def test_half_partial_rows(moe, T):
     half = moe.kernel_from_records(recs, *args, 64, half_rows=True)
     moe.check_status()
     assert half.dtype == torch.uint8 and tuple(half.shape) == (T, 15232)
+    # byte for byte the CPU restatement of the format applied to the float32 rows
+    assert np.array_equal(half.cpu().numpy(), oracle.encode_half_rows(full.cpu().numpy()))
     dec = decode_half_rows(half)
     gmax = full.view(T, 896, 8).abs().amax(dim=2, keepdim=True)
     # float16 keeps its own exponent per value: 11 significant bits of every value down to 2^-28 of the group maximum

@@ -109,3 +109,33 @@ def test_quantiser_restatement_matches_torch_formula(oracle):
     q_t = (xb * (1.0 / s_t).unsqueeze(2)).to(torch.float8_e4m3fn).view(9, 7168)
     assert torch.equal(s, s_t.t().contiguous())
     assert torch.equal(q.view(torch.uint8), q_t.view(torch.uint8))
+
+
+def test_half_row_restatement(oracle):
+    """The numpy restatement of the half form of un-rounded rows (include/b200moe.h, ``partial_format``): layout, scale
+    byte = exponent of the group maximum, 11 significant bits per value, zero and tiny groups, and agreement with
+    torch's own float32 -> float16 conversion.  The GPU tests require the library's bytes to equal this restatement."""
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((6, 7168)) * np.exp(rng.uniform(-30, 30, (6, 896)).repeat(8, axis=1))).astype(np.float32)
+    x[0, :16] = 0.0                                   # all-zero groups
+    x[1, 8:16] = [3e-38, 0, 0, 0, 0, 0, 0, 0]         # below 2^-113: flushed to zero by the clamp at 14
+    x[2, 0:8] = [1.0, 2.0 ** -10, 2.0 ** -20, -(2.0 ** -27), 0.3, -0.7, 2.0 ** -30, 0.0]
+    enc = oracle.encode_half_rows(x)
+    assert enc.shape == (6, 15232) and enc.dtype == np.uint8
+    eb = enc[:, 14336:].astype(np.int64)
+    g = x.reshape(6, 896, 8)
+    gmax = np.abs(g).max(axis=2)
+    big = gmax >= 2.0 ** -113
+    assert (eb[big] == (np.frexp(gmax[big])[1] - 1 + 127)).all() and (eb[~big] == 14).all()
+    dec = oracle.decode_half_rows(enc).reshape(6, 896, 8)
+    assert (dec[~big] == 0).all()
+    err = np.abs(dec - g)[big]
+    bound = (np.abs(g) * 2.0 ** -11 + gmax[:, :, None] * 2.0 ** -39)[big]
+    assert (err <= bound).all()
+    # the scaled values are what torch converts to float16 as well
+    k = np.ldexp(np.float32(1.0), (141 - eb)).astype(np.float32)
+    want = torch.from_numpy(g * k[:, :, None]).to(torch.float16).numpy().view(np.uint8).reshape(6, 14336)
+    assert (enc[:, :14336] == want).all()
+    # the largest magnitude of a group lands in [2^14, 2^15]
+    top = np.abs(enc[:, :14336].copy().view(np.float16).reshape(6, 896, 8).astype(np.float32)).max(axis=2)
+    assert ((top[big] >= 2.0 ** 14) & (top[big] <= 2.0 ** 15)).all()
