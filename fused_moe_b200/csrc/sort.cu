@@ -197,8 +197,16 @@ struct OutSegments {
 // Writes bf16 to `out` and/or the un-rounded sums to `out_f32` (either may be null).  topk_w == nullptr means weight 1
 // (the expert-parallel combine adds rows that are already weighted).
 // G = groups of eight columns a thread takes per round: 4 when the source rows are in the half form and a CTA owns a
-// whole token (64 contiguous bytes of float16 and ONE 4-byte load for the four scale bytes per source row, instead
-// of a 16-byte and a 1-byte load per group), else 1.
+// whole token, else 1.  With G = 4 a thread takes four ADJACENT groups: 64 contiguous bytes of float16 and one 4-byte
+// word of scale bytes per source row (measured at T = 16384 / 256 experts: 397 us, against 496 with one group per
+// thread and round and 533 with the four groups interleaved over the lanes of a warp).  Stores of half rows are another
+// matter when the row lives in another GPU's memory: 16 bytes at a 64-byte stride per lane and instruction made the
+// return of partial rows 1.6 x slower than whole 512-byte runs per instruction, so the encoded groups of a warp pass
+// through shared memory (swizzled, conflict-free both ways) and leave in lane order.
+__device__ __forceinline__ int swizzled_slot(int slot) {   // slot = 4 * lane + group; 16-byte units of a warp's 2 KB
+  const int l = slot >> 2;
+  return (slot & ~3) | ((slot & 3) ^ ((l >> 1) & 3));
+}
 template <int G>
 __global__ void __launch_bounds__(128)
 k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_map, const float* __restrict__ topk_w,
@@ -220,6 +228,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
   }
   __shared__ int s_pos[TOP_K];
   __shared__ float s_w[TOP_K];
+  __shared__ uint4 s_stage[G > 1 ? 4 : 1][G > 1 ? 128 : 1];   // G = 4: one warp's encoded groups on their way out
   pdl_launch_dependents();
   pdl_wait();
   // This is the last kernel of a layer call: if an earlier kernel of the call gave up on a wait, copy the status word
@@ -305,6 +314,26 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
       acc[0][4] = fmaf(w, b.x, acc[0][4]); acc[0][5] = fmaf(w, b.y, acc[0][5]);
       acc[0][6] = fmaf(w, b.z, acc[0][6]); acc[0][7] = fmaf(w, b.w, acc[0][7]);
     }
+    if (G > 1 && dst_row && half_rows) {
+      // encode, pass the warp's 128 groups through shared memory, store them in lane order (512 contiguous bytes per
+      // instruction); the scale bytes of a thread's four groups are one aligned word
+      uint8_t* row = reinterpret_cast<uint8_t*>(dst_row);
+      const int lane = threadIdx.x & 31;
+      uint4* stage = s_stage[threadIdx.x >> 5];
+      uint32_t sc4 = 0;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        uint32_t eb;
+        stage[swizzled_slot(4 * lane + g)] = encode_half_group(acc[g], eb);
+        sc4 |= eb << (8 * g);
+      }
+      __syncwarp();
+      const int first = (u >> 5) * 128;   // the warp's first group
+#pragma unroll
+      for (int g = 0; g < G; ++g) reinterpret_cast<uint4*>(row)[first + 32 * g + lane] = stage[swizzled_slot(32 * g + lane)];
+      __syncwarp();
+      reinterpret_cast<uint32_t*>(row + HALF_ROW_SCALES)[u] = sc4;
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int v = G * u + g;
@@ -318,7 +347,7 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
         reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
       }
       if (dst_row && half_rows) {
-        store_half_group(reinterpret_cast<uint8_t*>(dst_row), v, acc[g]);
+        if (G == 1) store_half_group(reinterpret_cast<uint8_t*>(dst_row), v, acc[g]);
       } else if (dst_row) {
         float4* dst = reinterpret_cast<float4*>(dst_row) + 2 * v;
         dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
@@ -330,7 +359,8 @@ k_reduce(const float* __restrict__ expert_out, const int* __restrict__ scatter_m
 }
 
 // out[t, :] = bf16(sum over the token's returned half rows, in slot order): the expert-parallel combine when the
-// partial rows travelled in the half form.  Same work split as k_reduce.
+// partial rows travelled in the half form.  Same work split as k_reduce (G groups of eight columns per thread).
+template <int G>
 __global__ void __launch_bounds__(128)
 k_combine_half(const uint8_t* __restrict__ rows, const int* __restrict__ slot_map, int T, uint16_t* __restrict__ out) {
   const int t = blockIdx.x;
@@ -339,24 +369,47 @@ k_combine_half(const uint8_t* __restrict__ rows, const int* __restrict__ slot_ma
   pdl_wait();
   if (threadIdx.x < TOP_K) s_pos[threadIdx.x] = __ldg(slot_map + static_cast<size_t>(t) * TOP_K + threadIdx.x);
   __syncthreads();
-  const int per = (H / 8) / gridDim.y;
-  for (int v = blockIdx.y * per + threadIdx.x; v < (blockIdx.y + 1) * per; v += blockDim.x) {
-    float acc[8];
+  const int per = (H / 8 / G) / gridDim.y;
+  for (int u = blockIdx.y * per + threadIdx.x; u < (blockIdx.y + 1) * per; u += blockDim.x) {
+    float acc[G][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < TOP_K; ++k) {
       const int pos = s_pos[k];
       if (pos < 0) continue;
-      fma_half_group(rows + static_cast<size_t>(pos) * HALF_ROW_BYTES, v, 1.0f, acc);
-    }
-    uint32_t o[4];
+      const uint8_t* row = rows + static_cast<size_t>(pos) * HALF_ROW_BYTES;
+      if (G == 1) {
+        fma_half_group(row, u, 1.0f, acc[0]);
+        continue;
+      }
+      // four adjacent groups per thread: 64 contiguous bytes and one word of scale bytes (see k_reduce)
+      const uint32_t sc4 = __ldg(reinterpret_cast<const uint32_t*>(row + HALF_ROW_SCALES) + u);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-      o[j] = *reinterpret_cast<uint32_t*>(&b);
+      for (int g = 0; g < G; ++g) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + G * u + g);
+        const float kw = __uint_as_float((((sc4 >> (8 * g)) & 0xffu) - 14u) << 23);
+        const uint32_t x[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x[j]));
+          acc[g][2 * j] = fmaf(f.x, kw, acc[g][2 * j]);
+          acc[g][2 * j + 1] = fmaf(f.y, kw, acc[g][2 * j + 1]);
+        }
+      }
     }
-    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(acc[g][2 * j], acc[g][2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[G * u + g] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
 }
 
@@ -378,7 +431,8 @@ int launch_reduce_rows(const float* rows, const int* slot_map, int T, uint16_t* 
   return B200MOE_OK;
 }
 int launch_combine_half(const void* rows, const int* slot_map, int T, uint16_t* out, cudaStream_t st) {
-  B200MOE_CUDA_TRY(launch_pdl(k_combine_half, dim3(T, reduce_splits(T)), dim3(128), 0, st,
+  auto kern = reduce_splits(T) == 1u ? k_combine_half<4> : k_combine_half<1>;
+  B200MOE_CUDA_TRY(launch_pdl(kern, dim3(T, reduce_splits(T)), dim3(128), 0, st,
                               static_cast<const uint8_t*>(rows), slot_map, T, out));
   return B200MOE_OK;
 }

@@ -351,10 +351,16 @@ def test_expert_parallel_half_rows_world1(moe):
     from fused_moe_b200 import ep, synth
     inp = gpu_inputs(300, 32, 4, 64, True)
     wts = _world1_weights(inp)
-    shards = {t: ep.make_cuda_shard(wts, rank=0, world=1, transport=t, max_tokens_per_rank=512, partial_rows="half")
+    _half_rows_world1(moe, ep, synth, inp, wts, 512, ((300, 4), (150, 9), (412, 12)))
+    # more than 512 rows: the reduce and the combine then take four groups per thread (one token per CTA)
+    _half_rows_world1(moe, ep, synth, inp, wts, 2048, ((1200, 5), (700, 6)))
+
+
+def _half_rows_world1(moe, ep, synth, inp, wts, capacity, batches):
+    shards = {t: ep.make_cuda_shard(wts, rank=0, world=1, transport=t, max_tokens_per_rank=capacity, partial_rows="half")
               for t in ("nccl", "peer")}
     # batches above the token-minor GEMM limit, where the shard's 256-expert layer adds in kernel()'s order
-    for T, seed in ((300, 4), (150, 9), (412, 12)):
+    for T, seed in batches:
         cur = synth.make_inputs(T, 32, seed=seed, local_expert_offset=64, skew=True, device="cuda", weights=inp)
         want = moe.kernel(**cur).float()
         got = {}
