@@ -21,7 +21,7 @@ where ranking, packing, the local experts and the final add are kernels of libb2
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Optional, Tuple
+from typing import Callable, Optional
 
 import os
 
